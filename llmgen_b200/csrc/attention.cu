@@ -24,7 +24,9 @@
 // Variations a model may switch on: values of another width than keys (`vd`); a bound on the scores,
 // s <- softcap * tanh(s / softcap) after the scale; a sink, one more term exp(0) in the softmax's denominator (a key of
 // score 0 that has no value: the weights of a row then sum to less than one; it enters once, when a row is finished or
-// its parts are merged); an output gate, out <- out * sigmoid(gate) element by element, applied as the row is written.
+// its parts are merged); an output gate, out <- out * sigmoid(gate) element by element, applied as the row is written;
+// a mask in blocks of `chunk` positions counted from the sequence's start: a query sees the keys at or before it that lie
+// in its own block, floor(k / chunk) = floor(q / chunk) (with key parts, the visible keys of a single token are what is split).
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()
@@ -47,7 +49,7 @@ struct AttnParams {
     float* part_ml;
     const void* gate;        // [tokens, nq * vd] of the storage type, rows `gate_stride` apart, or null
     long long q_stride, o_stride, gate_stride;
-    int max_blocks, nq, nkv, hd, vd, page_size, window, num_parts, part_size, bq, gc, chunks, sink;
+    int max_blocks, nq, nkv, hd, vd, page_size, window, num_parts, part_size, bq, gc, chunks, sink, chunk;
     float scale, softcap;
 };
 
@@ -78,14 +80,16 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
     if (!padding) {
         k_end = first_pos + nq_tile;
         k_beg = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+        if (p.chunk > 0) k_beg = max(k_beg, first_pos / p.chunk * p.chunk);     // the block of the tile's first query
     }
     if (p.num_parts > 1) {
         // part_size <= 0: split this sequence's own keys evenly (whole key tiles per part), so the
         // launch shape does not depend on the context lengths.
         int part_size = p.part_size;
-        if (part_size <= 0) part_size = ceil_div(ceil_div(max(ctx, 1), p.num_parts), KT) * KT;
-        k_beg = max(k_beg, part * part_size);
-        k_end = min(k_end, (part + 1) * part_size);
+        if (part_size <= 0) part_size = ceil_div(ceil_div(max(p.chunk > 0 ? k_end - k_beg : ctx, 1), p.num_parts), KT) * KT;
+        const int base = p.chunk > 0 ? k_beg : 0;      // blocks of positions: the parts cut what the tile can see
+        k_beg = max(k_beg, base + part * part_size);
+        k_end = min(k_end, base + (part + 1) * part_size);
     }
     const T* qbase = static_cast<const T*>(p.q);
     const T* kc = static_cast<const T*>(p.kcache);
@@ -193,7 +197,8 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int qpos = first_pos + qi_of[i];
-            const bool ok = valid[i] && kpos < k_end && kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
+            const bool ok = valid[i] && kpos < k_end && kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window) &&
+                            (p.chunk <= 0 || kpos >= qpos / p.chunk * p.chunk);
             const float sv = ok ? sc[i] : -INFINITY;
             const float tmax = warp_max(sv);
             const float m_new = fmaxf(m[i], tmax);
@@ -335,7 +340,7 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
                                      const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int hd,
                                      int page_size, int window, float scale, int num_parts, int part_size,
                                      void* scratch, int vd, float softcap, int sink, const void* gate, long long gate_stride,
-                                     int dtype, void* stream) {
+                                     int chunk, int dtype, void* stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return LLMK_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0) LLMK_FAIL("paged_attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
     if (hd <= 0 || hd > 512) LLMK_FAIL("paged_attention: head_dim %d must be positive, at most 512", hd);
@@ -343,6 +348,7 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
     if (vd > 512) LLMK_FAIL("paged_attention: value width %d must be at most 512", vd);
     if (softcap < 0.f) LLMK_FAIL("paged_attention: softcap %g", (double)softcap);
     if (page_size <= 0) LLMK_FAIL("paged_attention: page_size %d", page_size);
+    if (chunk < 0) LLMK_FAIL("paged_attention: blocks of %d positions", chunk);
     if (num_parts < 1 || (num_parts > 1 && !scratch)) LLMK_FAIL("paged_attention: bad split (%d parts, scratch %p)", num_parts, scratch);
     if (num_parts > 65535 || nkv > 65535) LLMK_FAIL("paged_attention: grid too large");
     AttnParams p;
@@ -354,7 +360,7 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
     p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
     p.q_stride = q_stride; p.o_stride = o_stride; p.max_blocks = max_blocks;
     p.nq = nq; p.nkv = nkv; p.hd = hd; p.vd = vd; p.page_size = page_size; p.window = window;
-    p.softcap = softcap; p.sink = sink ? 1 : 0; p.gate = gate; p.gate_stride = gate_stride;
+    p.softcap = softcap; p.sink = sink ? 1 : 0; p.gate = gate; p.gate_stride = gate_stride; p.chunk = chunk;
     p.num_parts = num_parts; p.part_size = part_size; p.scale = scale;
     p.part_o = (float*)scratch;
     p.part_ml = num_parts > 1 ? (float*)scratch + (size_t)n_tokens * nq * num_parts * vd : nullptr;

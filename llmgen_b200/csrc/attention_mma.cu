@@ -3,7 +3,7 @@
 // accumulators), everything between them on the CUDA cores in float32.
 //
 //   S = Q K^T      Q and K are the cache's bfloat16 values, every product exact, sums float32
-//   scores         s * scale, then (softcap > 0) softcap * tanh(s / softcap), the causal (and window) mask, the row's
+//   scores         s * scale, then (softcap > 0) softcap * tanh(s / softcap), the causal (and window, or block) mask, the row's
 //                  running maximum and sum, the weights exp(s - m): float32, `tanhf` and `exp2f` at full precision
 //   O += P V       a float32 weight enters as THREE bfloat16 terms p = p1 + p2 + p3 (24 bits of mantissa), so every
 //                  product with a bfloat16 value is what float32 arithmetic would give; three MMAs a step
@@ -33,7 +33,7 @@ struct Params {
     const int* tile_seq;
     const int* tile_q0;
     long long q_stride, o_stride, gate_stride;
-    int max_blocks, nq, nkv, page_size, window, sink;
+    int max_blocks, nq, nkv, page_size, window, sink, chunk;     // chunk > 0: a query sees the keys of its own block of that many positions
     float scale, softcap;
 };
 
@@ -95,7 +95,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(Params p) {
     }
     const int first_pos = ctx - q_len + q0;
     const int k_end = first_pos + nq_tile;
-    const int k_beg = p.window > 0 ? max(0, first_pos - p.window + 1) / BN * BN : 0;
+    int k_beg = p.window > 0 ? max(0, first_pos - p.window + 1) / BN * BN : 0;
+    if (p.chunk > 0) k_beg = max(k_beg, first_pos / p.chunk * p.chunk / BN * BN);
     const int* bt = p.block_tables + (size_t)s * p.max_blocks;
 
     for (int idx = threadIdx.x; idx < BM * (HD / 8); idx += blockDim.x) {
@@ -115,6 +116,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(Params p) {
     for (int n = 0; n < VD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     const int qpos[2] = {first_pos + warp * 16 + g, first_pos + warp * 16 + g + 8};
+    const int kmin[2] = {p.chunk > 0 ? qpos[0] / p.chunk * p.chunk : 0, p.chunk > 0 ? qpos[1] / p.chunk * p.chunk : 0};
     const float inv_cap = p.softcap > 0.f ? 1.0f / p.softcap : 0.f;
     constexpr float LOG2E = 1.4426950408889634f;
 
@@ -127,8 +129,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(Params p) {
             const int key = idx / VECS, v = idx % VECS;
             const int kpos = t0 + key;
             bf16* dst = v < HD / 8 ? Kd + key * QLD + v * 8 : Vd + key * VLD + (v - HD / 8) * 8;
-            if (kpos < k_end) {
-                const int page = bt[kpos / p.page_size];
+            const int page = kpos < k_end ? bt[kpos / p.page_size] : -1;      // -1 too: a page the window has passed
+            if (page >= 0) {
                 const size_t row = ((size_t)page * p.nkv + kvh) * p.page_size + kpos % p.page_size;
                 cp_async16(dst, v < HD / 8 ? p.kcache + row * HD + v * 8 : p.vcache + row * VD + (v - HD / 8) * 8);
             } else {
@@ -170,7 +172,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(Params p) {
                 const int kpos = t0 + n * 8 + 2 * tq + (e & 1);
                 float v = sc[n][e] * p.scale;
                 if (p.softcap > 0.f) v = p.softcap * tanh_abs(v * inv_cap);
-                const bool vis = kpos <= qpos[r] && kpos < k_end && (p.window <= 0 || kpos > qpos[r] - p.window);
+                const bool vis = kpos <= qpos[r] && kpos < k_end && (p.window <= 0 || kpos > qpos[r] - p.window) && kpos >= kmin[r];
                 v = vis ? v : -INFINITY;
                 sc[n][e] = v;
                 mx[r] = fmaxf(mx[r], v);
@@ -287,7 +289,7 @@ LLMK_EXPORT int llmk_attention_mma(void* out, long long o_stride, const void* q,
                                    const void* vcache, const int* block_tables, int max_blocks, const int* ctx_len, const int* cu_q,
                                    const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv, int hd, int vd,
                                    int page_size, int window, float scale, float softcap, int sink, const void* gate,
-                                   long long gate_stride, void* stream) {
+                                   long long gate_stride, int chunk, void* stream) {
     if (n_tiles <= 0) return LLMK_OK;
     if (llmk_attention_mma_tile_queries(nq, nkv, hd, vd) == 0)
         LLMK_FAIL("attention_mma: not taken (heads %d/%d, key width %d and value width %d must be 64 or 128)", nq, nkv, hd, vd);
@@ -299,7 +301,7 @@ LLMK_EXPORT int llmk_attention_mma(void* out, long long o_stride, const void* q,
     p.q = (const bf16*)q; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache; p.out = (bf16*)out;
     p.gate = (const bf16*)gate; p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q;
     p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.q_stride = q_stride; p.o_stride = o_stride; p.gate_stride = gate_stride;
-    p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.sink = sink ? 1 : 0;
+    p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.sink = sink ? 1 : 0; p.chunk = chunk > 0 ? chunk : 0;
     p.scale = scale; p.softcap = softcap;
     dim3 grid(n_tiles, nq);
     cudaStream_t s = (cudaStream_t)stream;

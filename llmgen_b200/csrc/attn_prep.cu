@@ -46,7 +46,7 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
                                  const float* __restrict__ sin_tab, const float* __restrict__ q_gain,
                                  const float* __restrict__ k_gain, int n_tokens, int nq, int nk, int nkv_cache,
                                  int hd, int rot, int page_size, float eps, float q_off, float k_off,
-                                 const float* __restrict__ bias, int vd) {
+                                 const float* __restrict__ bias, int vd, int interleaved, int norm_after) {
     const int lane = threadIdx.x & 31;
     const int warps_per_block = blockDim.x >> 5;
     const int heads = nq + 2 * nk;
@@ -100,10 +100,10 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
     if (splits == 0) {
 #pragma unroll
         for (int i = 0; i < MAX_PAIRS; ++i) {
-            const int p = lane + 32 * i;
+            const int p = lane + 32 * i, pa = interleaved ? 2 * p : p, pb = interleaved ? 2 * p + 1 : p + half;
             if (p < half) {
-                a[i] = to_float(x.x[p]);
-                b[i] = to_float(x.x[p + half]);
+                a[i] = to_float(x.x[pa]);
+                b[i] = to_float(x.x[pb]);
             }
         }
 #pragma unroll
@@ -122,10 +122,10 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
             const float* ps = x.p + (size_t)sp * split_stride;
 #pragma unroll
             for (int i = 0; i < MAX_PAIRS; ++i) {
-                const int p = lane + 32 * i;
+                const int p = lane + 32 * i, pa = interleaved ? 2 * p : p, pb = interleaved ? 2 * p + 1 : p + half;
                 if (p < half) {
-                    a[i] += __ldcg(ps + p);
-                    b[i] += __ldcg(ps + p + half);
+                    a[i] += __ldcg(ps + pa);
+                    b[i] += __ldcg(ps + pb);
                 }
             }
 #pragma unroll
@@ -138,10 +138,10 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
     if (hb) {
 #pragma unroll
         for (int i = 0; i < MAX_PAIRS; ++i) {
-            const int p = lane + 32 * i;
+            const int p = lane + 32 * i, pa = interleaved ? 2 * p : p, pb = interleaved ? 2 * p + 1 : p + half;
             if (p < half) {
-                a[i] += hb[p];
-                b[i] += hb[p + half];
+                a[i] += hb[pa];
+                b[i] += hb[pb];
             }
         }
 #pragma unroll
@@ -161,10 +161,10 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
         const float rinv = 1.0f / sqrtf(ss / (float)hd + eps);
 #pragma unroll
         for (int i = 0; i < MAX_PAIRS; ++i) {
-            const int p = lane + 32 * i;
+            const int p = lane + 32 * i, pa = interleaved ? 2 * p : p, pb = interleaved ? 2 * p + 1 : p + half;
             if (p < half) {
-                a[i] = a[i] * rinv * (gain[p] + goff);
-                b[i] = b[i] * rinv * (gain[p + half] + goff);
+                a[i] = a[i] * rinv * (gain[pa] + goff);
+                b[i] = b[i] * rinv * (gain[pb] + goff);
             }
         }
 #pragma unroll
@@ -187,6 +187,25 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
             }
         }
     }
+    if (norm_after) {
+        // no gains: the rotated head divided by its root mean square
+        float s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAX_PAIRS; ++i)
+            if (lane + 32 * i < half) s2 += a[i] * a[i] + b[i] * b[i];
+#pragma unroll
+        for (int i = 0; i < MAX_TAIL; ++i)
+            if (rot + lane + 32 * i < hd) s2 += tail[i] * tail[i];
+        s2 = warp_sum(s2);
+        const float rinv = 1.0f / sqrtf(s2 / (float)hd + eps);
+#pragma unroll
+        for (int i = 0; i < MAX_PAIRS; ++i) {
+            a[i] *= rinv;
+            b[i] *= rinv;
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_TAIL; ++i) tail[i] *= rinv;
+    }
     T* dst;
     if (is_q) {
         dst = q_out + (size_t)t * q_stride + (size_t)h * hd;
@@ -197,10 +216,10 @@ __global__ void attn_prep_kernel(const void* __restrict__ qkv, long long row_str
     }
 #pragma unroll
     for (int i = 0; i < MAX_PAIRS; ++i) {
-        const int p = lane + 32 * i;
+        const int p = lane + 32 * i, pa = interleaved ? 2 * p : p, pb = interleaved ? 2 * p + 1 : p + half;
         if (p < half) {
-            dst[p] = from_float<T>(a[i]);
-            dst[p + half] = from_float<T>(b[i]);
+            dst[pa] = from_float<T>(a[i]);
+            dst[pb] = from_float<T>(b[i]);
         }
     }
 #pragma unroll
@@ -481,9 +500,14 @@ LLMK_EXPORT int llmk_attn_prep(const void* qkv, long long row_stride, int splits
     if (n_tokens <= 0) return LLMK_OK;
     if (vd <= 0) vd = hd;
     if (vd > 32 * MAX_TAIL) LLMK_FAIL("attn_prep: value width %d too large", vd);
-    if (pairing != LLMK_PAIR_HALF_SPLIT)
-        LLMK_FAIL("attn_prep: rotary pairing %d is not built (0: half-split, pairs (i, i + rot / 2))", pairing);
-    if (head_norm != LLMK_HEAD_NORM_RMS) LLMK_FAIL("attn_prep: per-head norm kind %d is not built (0: RMSNorm)", head_norm);
+    if (pairing != LLMK_PAIR_HALF_SPLIT && pairing != LLMK_PAIR_INTERLEAVED)
+        LLMK_FAIL("attn_prep: rotary pairing %d is not built (0: half-split, pairs (i, i + rot / 2); 1: pairs (2i, 2i + 1))", pairing);
+    if (head_norm != LLMK_HEAD_NORM_RMS && head_norm != LLMK_HEAD_NORM_UNIT_AFTER)
+        LLMK_FAIL("attn_prep: per-head norm kind %d is not built (0: RMSNorm before the rotation; 1: without gains, after it)", head_norm);
+    if (head_norm == LLMK_HEAD_NORM_UNIT_AFTER && (q_gain || k_gain)) LLMK_FAIL("attn_prep: the norm after the rotation has no gains");
+    // the 16-byte variants pair values half a head apart and norm before they rotate
+    const bool general_only = pairing != LLMK_PAIR_HALF_SPLIT || head_norm != LLMK_HEAD_NORM_RMS;
+    const int interleaved = pairing == LLMK_PAIR_INTERLEAVED ? 1 : 0, norm_after = head_norm == LLMK_HEAD_NORM_UNIT_AFTER ? 1 : 0;
     if (hd <= 0 || hd % 2 != 0 || hd > 512) LLMK_FAIL("attn_prep: head_dim %d must be even and at most 512", hd);
     if (rot < 0 || rot > hd || rot % 2 != 0) LLMK_FAIL("attn_prep: rotary width %d must be even and at most head_dim %d", rot, hd);
     if (rot / 2 > 32 * MAX_PAIRS || hd - rot > 32 * MAX_TAIL) LLMK_FAIL("attn_prep: head_dim %d / rotary width %d too large", hd, rot);
@@ -499,7 +523,7 @@ LLMK_EXPORT int llmk_attn_prep(const void* qkv, long long row_stride, int splits
     const long long blocks = (items + warps - 1) / warps;
     if (blocks > 2147483647LL) LLMK_FAIL("attn_prep: too many rows");
     cudaError_t e;
-    if (splits == 0 && n_tokens >= 32 && !bias && vd == hd) {
+    if (splits == 0 && n_tokens >= 32 && !bias && vd == hd && !general_only) {
         bool taken = false;
         if (dtype == LLMK_F32)
             taken = launch_vec<float>(qkv, row_stride, q_out, q_stride, kcache, vcache, positions, slots, cos_tab, sin_tab,
@@ -516,12 +540,12 @@ LLMK_EXPORT int llmk_attn_prep(const void* qkv, long long row_stride, int splits
         e = llmk_launch(attn_prep_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, s, true, qkv, row_stride,
                         splits, split_stride, (float*)q_out, q_stride, (float*)kcache, (float*)vcache, positions, slots,
                         cos_tab, sin_tab, q_gain, k_gain, n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off,
-                        k_off, bias, vd);
+                        k_off, bias, vd, interleaved, norm_after);
     else if (dtype == LLMK_BF16)
         e = llmk_launch(attn_prep_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), 0, s, true, qkv, row_stride,
                         splits, split_stride, (bf16*)q_out, q_stride, (bf16*)kcache, (bf16*)vcache, positions, slots,
                         cos_tab, sin_tab, q_gain, k_gain, n_tokens, nq, nk, nkv_cache, hd, rot, page_size, eps, q_off,
-                        k_off, bias, vd);
+                        k_off, bias, vd, interleaved, norm_after);
     else
         LLMK_FAIL("attn_prep: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("attn_prep", e);

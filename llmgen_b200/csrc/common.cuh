@@ -24,7 +24,8 @@ enum { LLMK_F32 = 0, LLMK_BF16 = 1 };
 // How a rotary encoding pairs the values of a head, and which norm runs over a head of q and k before it:
 // kernels take the codes and refuse the ones they do not implement.
 enum { LLMK_PAIR_HALF_SPLIT = 0, LLMK_PAIR_INTERLEAVED = 1 };
-enum { LLMK_HEAD_NORM_RMS = 0 };
+// LLMK_HEAD_NORM_UNIT_AFTER: no gains, and after the rotation: x / sqrt(mean(x^2) + eps) over the rotated head.
+enum { LLMK_HEAD_NORM_RMS = 0, LLMK_HEAD_NORM_UNIT_AFTER = 1 };
 
 typedef __nv_bfloat16 bf16;
 

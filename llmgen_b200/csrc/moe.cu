@@ -1,8 +1,9 @@
 // A routed feed-forward (mixture of experts) without a trip to the host, so that a step holding one can be
 // recorded into a CUDA graph: every launch has a shape that follows from (tokens, experts, top) alone.
 //
-//   moe_route     per token: z = Wr h (float32), s = sigmoid(z) or softmax(z), the `top` largest s choose experts;
-//                 slot t * top + c holds (expert, weight)
+//   moe_route     per token: z = Wr h (+ b) (float32), s = sigmoid(z) or softmax(z), the `top` largest s choose experts;
+//                 slot t * top + c holds (expert, weight); or the `top` largest z choose and the weights are the softmax
+//                 over the chosen z alone
 //   moe_plan      one block: slots grouped by expert, cut into tiles of TT rows of one expert each; the list of tiles
 //                 has a fixed length (slots / TT + experts), padded with expert -1
 //   moe_experts   grid (tiles, column blocks): first product of a tile's rows with its expert's matrices and the
@@ -14,7 +15,8 @@
 //   moe_combine   per token: shared expert's output (if any) + its slots' outputs in slot order
 //
 // The weight multiplies the expert's input (mode "input") or its output (mode "output").
-// Gated activation: g' = min(g, L), u' = clamp(u, -L, L), y = g' sigmoid(alpha g') (u' + 1)   (L <= 0: no clamp).
+// Gated activation: g' = min(g, L), u' = clamp(u, -L, L), y = g' sigmoid(alpha g') (u' + 1)   (L <= 0: no clamp),
+// or the plain gated unit y = g sigmoid(g) u.
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()
@@ -24,11 +26,13 @@ constexpr int MOE_KC = 256;     // input values per pass through shared memory
 
 // ---------------------------------------------------------------------------------------------- route
 // One block per token: the warps share the experts (a warp per dot product, float32 sums in a fixed order), warp 0 then
-// scores and picks.  scoring 0: sigmoid, 1: softmax over all experts.
+// scores and picks.  scoring 0: sigmoid, 1: softmax over all experts, 2: the logits themselves choose, and the weights
+// are the softmax over the chosen logits.
 template <typename T>
 __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ wr,
-                                                        int* __restrict__ slot_expert, float* __restrict__ slot_weight, int K, int E,
-                                                        int top, int scoring, int renorm) {
+                                                        const float* __restrict__ bias, int* __restrict__ slot_expert,
+                                                        float* __restrict__ slot_weight, int K, int E, int top, int scoring,
+                                                        int renorm) {
     extern __shared__ float sm[];   // [K] the row in float32, [E] scores
     float* xs = sm;
     float* s = sm + K;
@@ -53,11 +57,13 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
             for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], w[k], acc);
         }
         acc = warp_sum(acc);
-        if (lane == 0) s[e] = acc;
+        if (lane == 0) s[e] = acc + (bias ? bias[e] : 0.f);
     }
     __syncthreads();
     if (warp != 0) return;
-    if (scoring == 1) {
+    if (scoring == 2) {
+        // the logits choose
+    } else if (scoring == 1) {
         float mx = -INFINITY;
         for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
         mx = warp_max(mx);
@@ -92,15 +98,25 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
         }
         __syncwarp();
     }
+    if (scoring == 2) {
+        // softmax over the chosen logits; the first chosen is the largest
+        if (lane == 0) {
+            const float mx = slot_weight[t * top];
+            float sum = 0.f;
+            for (int c = 0; c < top; ++c) sum += expf(slot_weight[t * top + c] - mx);
+            for (int c = 0; c < top; ++c) slot_weight[t * top + c] = expf(slot_weight[t * top + c] - mx) / sum;
+        }
+        return;
+    }
     if (renorm && lane == 0)
         for (int c = 0; c < top; ++c) slot_weight[t * top + c] /= total;
 }
 
-LLMK_EXPORT int llmk_moe_route(const void* h, long long ldh, const float* wr, int* slot_expert, float* slot_weight, int n_tokens,
-                               int K, int E, int top, int scoring, int renorm, int dtype, void* stream) {
+LLMK_EXPORT int llmk_moe_route(const void* h, long long ldh, const float* wr, const float* bias, int* slot_expert, float* slot_weight,
+                               int n_tokens, int K, int E, int top, int scoring, int renorm, int dtype, void* stream) {
     if (n_tokens <= 0) return LLMK_OK;
     if (E <= 0 || top <= 0 || top > E || K <= 0) LLMK_FAIL("moe_route: bad sizes (experts %d, top %d, width %d)", E, top, K);
-    if (scoring != 0 && scoring != 1) LLMK_FAIL("moe_route: unknown scoring %d", scoring);
+    if (scoring < 0 || scoring > 2) LLMK_FAIL("moe_route: unknown scoring %d", scoring);
     const size_t smem = ((size_t)K + E) * sizeof(float);
     if (smem > 200 * 1024) LLMK_FAIL("moe_route: a row of %d values and %d experts do not fit shared memory", K, E);
     const int threads = E >= 8 ? 256 : 32 * E;
@@ -108,11 +124,11 @@ LLMK_EXPORT int llmk_moe_route(const void* h, long long ldh, const float* wr, in
     cudaError_t e;
     if (dtype == LLMK_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = llmk_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, true, (const float*)h, ldh, wr, slot_expert,
+        e = llmk_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, true, (const float*)h, ldh, wr, bias, slot_expert,
                         slot_weight, K, E, top, scoring, renorm);
     } else if (dtype == LLMK_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = llmk_launch(moe_route_kernel<bf16>, dim3(n_tokens), dim3(threads), smem, s, true, (const bf16*)h, ldh, wr, slot_expert,
+        e = llmk_launch(moe_route_kernel<bf16>, dim3(n_tokens), dim3(threads), smem, s, true, (const bf16*)h, ldh, wr, bias, slot_expert,
                         slot_weight, K, E, top, scoring, renorm);
     } else
         LLMK_FAIL("moe_route: unknown dtype %d", dtype);
@@ -239,7 +255,7 @@ __global__ void __launch_bounds__(128) moe_experts_kernel(float* __restrict__ ou
                                                           const int* __restrict__ order, const float* __restrict__ slot_weight,
                                                           const int* __restrict__ tile_expert, const int* __restrict__ tile_start,
                                                           const int* __restrict__ tile_rows, int top, int K, int N, int scale_rows,
-                                                          float alpha, float limit) {
+                                                          float alpha, float limit, int plain) {
     __shared__ float xs[MOE_TT][MOE_KC];
     __shared__ int src_row[MOE_TT];
     __shared__ float row_w[MOE_TT];
@@ -300,11 +316,15 @@ __global__ void __launch_bounds__(128) moe_experts_kernel(float* __restrict__ ou
         float v;
         if (FIRST) {
             float g = acc0[i], u = acc1[i];
-            if (limit > 0.f) {
-                g = fminf(g, limit);
-                u = fminf(fmaxf(u, -limit), limit);
+            if (plain) {
+                v = g / (1.0f + expf(-g)) * u;
+            } else {
+                if (limit > 0.f) {
+                    g = fminf(g, limit);
+                    u = fminf(fmaxf(u, -limit), limit);
+                }
+                v = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
             }
-            v = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
         } else {
             v = acc0[i] * row_w[i];
         }
@@ -312,6 +332,7 @@ __global__ void __launch_bounds__(128) moe_experts_kernel(float* __restrict__ ou
     }
 }
 
+// plain != 0: the gated unit is silu(g) u (alpha and limit unused).
 // first != 0: in = h [tokens, width] of the storage dtype, w0 / w1 = gate / up [E, ff, width], out = y [slots, ff]; the rows
 //             are multiplied by their weights when weight_on_input.
 // first == 0: in = y [slots, ff] float32, w0 = down [E, width, ff], out [slots, width]; multiplied by the weights
@@ -319,7 +340,7 @@ __global__ void __launch_bounds__(128) moe_experts_kernel(float* __restrict__ ou
 LLMK_EXPORT int llmk_moe_experts(float* out, const void* in, long long ld_in, const void* w0, const void* w1, const int* order,
                                  const float* slot_weight, const int* tile_expert, const int* tile_start, const int* tile_rows,
                                  int n_slots, int E, int top, int K, int N, int first, int weight_on_input, float alpha, float limit,
-                                 int dtype, void* stream) {
+                                 int plain, int dtype, void* stream) {
     if (n_slots <= 0) return LLMK_OK;
     dim3 grid(llmk_moe_max_tiles(n_slots, E, 0), ceil_div(N, 128));
     cudaStream_t s = (cudaStream_t)stream;
@@ -328,17 +349,17 @@ LLMK_EXPORT int llmk_moe_experts(float* out, const void* in, long long ld_in, co
     if (dtype == LLMK_F32) {
         if (first)
             e = llmk_launch(moe_experts_kernel<float, true>, grid, dim3(128), 0, s, true, out, in, ld_in, (const float*)w0, (const float*)w1, order,
-                            slot_weight, tile_expert, tile_start, tile_rows, top, K, N, scale_rows, alpha, limit);
+                            slot_weight, tile_expert, tile_start, tile_rows, top, K, N, scale_rows, alpha, limit, plain);
         else
             e = llmk_launch(moe_experts_kernel<float, false>, grid, dim3(128), 0, s, true, out, in, ld_in, (const float*)w0, (const float*)w1, order,
-                            slot_weight, tile_expert, tile_start, tile_rows, top, K, N, scale_rows, alpha, limit);
+                            slot_weight, tile_expert, tile_start, tile_rows, top, K, N, scale_rows, alpha, limit, plain);
     } else if (dtype == LLMK_BF16) {
         if (first)
             e = llmk_launch(moe_experts_kernel<bf16, true>, grid, dim3(128), 0, s, true, out, in, ld_in, (const bf16*)w0, (const bf16*)w1, order,
-                            slot_weight, tile_expert, tile_start, tile_rows, top, K, N, scale_rows, alpha, limit);
+                            slot_weight, tile_expert, tile_start, tile_rows, top, K, N, scale_rows, alpha, limit, plain);
         else
             e = llmk_launch(moe_experts_kernel<bf16, false>, grid, dim3(128), 0, s, true, out, in, ld_in, (const bf16*)w0, (const bf16*)w1, order,
-                            slot_weight, tile_expert, tile_start, tile_rows, top, K, N, scale_rows, alpha, limit);
+                            slot_weight, tile_expert, tile_start, tile_rows, top, K, N, scale_rows, alpha, limit, plain);
     } else
         LLMK_FAIL("moe_experts: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("moe_experts", e);
@@ -346,10 +367,12 @@ LLMK_EXPORT int llmk_moe_experts(float* out, const void* in, long long ld_in, co
 }
 
 // -------------------------------------------------------------------------------------------- combine
-// out[t, c] (float32) = (shared ? shared[t, c] : 0) + sum over the token's slots, in slot order, of rows[pos_of_slot, c].
+// out[t, c] (float32) = (shared ? shared[t, c] : 0) + sum over the token's slots, in slot order, of rows[pos_of_slot, c]
+// (times the slot's weight where `slot_weight` is given: the weight on an expert's output).
 template <typename T>
 __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restrict__ rows, const int* __restrict__ pos_of_slot,
-                                   const T* __restrict__ shared_out, int n_tokens, int top, int H) {
+                                   const T* __restrict__ shared_out, const float* __restrict__ slot_weight, int n_tokens, int top,
+                                   int H) {
     pdl_launch_dependents();
     pdl_wait();
     const long long total = (long long)n_tokens * H;
@@ -359,14 +382,14 @@ __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restr
         float v = shared_out ? to_float(shared_out[i]) : 0.f;
         for (int k = 0; k < top; ++k) {
             const int pos = pos_of_slot[t * top + k];
-            if (pos >= 0) v += rows[(size_t)pos * H + c];
+            if (pos >= 0) v += slot_weight ? slot_weight[t * top + k] * rows[(size_t)pos * H + c] : rows[(size_t)pos * H + c];
         }
         out[i] = v;
     }
 }
 
-LLMK_EXPORT int llmk_moe_combine(float* out, const float* rows, const int* pos_of_slot, const void* shared_out, int n_tokens, int top,
-                                 int H, int dtype, void* stream) {
+LLMK_EXPORT int llmk_moe_combine(float* out, const float* rows, const int* pos_of_slot, const void* shared_out, const float* slot_weight,
+                                 int n_tokens, int top, int H, int dtype, void* stream) {
     if (n_tokens <= 0) return LLMK_OK;
     long long blocks = ((long long)n_tokens * H + 255) / 256;
     if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
@@ -374,10 +397,10 @@ LLMK_EXPORT int llmk_moe_combine(float* out, const float* rows, const int* pos_o
     cudaError_t e;
     if (dtype == LLMK_F32)
         e = llmk_launch(moe_combine_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, out, rows, pos_of_slot, (const float*)shared_out,
-                        n_tokens, top, H);
+                        slot_weight, n_tokens, top, H);
     else if (dtype == LLMK_BF16)
         e = llmk_launch(moe_combine_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, true, out, rows, pos_of_slot, (const bf16*)shared_out,
-                        n_tokens, top, H);
+                        slot_weight, n_tokens, top, H);
     else
         LLMK_FAIL("moe_combine: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("moe_combine", e);

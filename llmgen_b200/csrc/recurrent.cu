@@ -8,6 +8,11 @@
 //   rglru_scan          that recurrence over each sequence's new tokens, times the other branch's gelu
 //   delta_scan          the gated delta rule with a decay per key channel:
 //                       S <- diag(g) S;  d = beta (v - S^T k);  S <- S + k d^T;  o = S^T q
+//   token_shift_mix     several blends of every token's row with the row of the token before it, the last row of a
+//                       sequence kept in its state:  m_i[t] = x[t] + (x[t-1] - x[t]) mu_i
+//   decay_scan          linear attention with a decay per key channel, in two orders of a token's steps:
+//                       S <- diag(a) S + k v^T;  o = S^T q                       (read after the update)
+//                       o = (S + diag(u) k v^T)^T q;  S <- diag(a) S + k v^T     (read before it, a bonus on the own key)
 //
 // A step's sequences are given as everywhere else: sequence s owns token rows [cu_q[s], cu_q[s+1]), its state lies in
 // slot state_slots[s] (-1: none; the sequence then starts from zeros and leaves nothing).  Rows beyond cu_q[n_seqs]
@@ -776,5 +781,256 @@ LLMK_EXPORT int llmk_delta_scan(float* out, float* qkv, long long qkv_ld, const 
     else if (D <= 128) e = launch_delta<8, 16>(p, n_seqs, s);
     else e = launch_delta<16, 16>(p, n_seqs, s);
     LLMK_CHECK_LAUNCH_RC("delta_scan", e);
+    return LLMK_OK;
+}
+
+
+// ------------------------------------------------------------------------------------------------ token shift
+// out[i][t, c] = x[t, c] + (prev(t)[c] - x[t, c]) * mu[i][c] for i < n_mix, prev(t) the row of the token before t in its
+// sequence: the row above inside a step, the state's row for a step's first token (zeros for a fresh request).  The thread
+// that reads a sequence's state row also leaves the sequence's last row there, after reading, so that no other thread's
+// read meets the write.
+template <typename T>
+__global__ void token_shift_mix_kernel(T* __restrict__ out, long long out_plane, const T* __restrict__ x, long long x_ld,
+                                       const float* __restrict__ mu, float* __restrict__ state, long long state_ld,
+                                       const int* __restrict__ cu_q, const int* __restrict__ state_slots, int n_seqs, int W,
+                                       int n_mix) {
+    const int t = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (c >= W) return;
+    const int s = seq_of_row(cu_q, n_seqs, t);
+    if (s < 0) return;
+    const int q_beg = cu_q[s], q_end = cu_q[s + 1];
+    const float cur = to_float(x[(size_t)t * x_ld + c]);
+    float prev;
+    if (t > q_beg) {
+        prev = to_float(x[(size_t)(t - 1) * x_ld + c]);
+    } else {
+        const int slot = state_slots[s];
+        float* st = slot >= 0 ? state + (size_t)slot * state_ld + c : nullptr;
+        prev = st ? *st : 0.f;
+        if (st) *st = to_float(x[(size_t)(q_end - 1) * x_ld + c]);
+    }
+    const float d = prev - cur;
+    for (int i = 0; i < n_mix; ++i)
+        out[(size_t)i * out_plane + (size_t)t * W + c] = from_float<T>(fmaf(d, mu[(size_t)i * W + c], cur));
+}
+
+// out: [n_mix] planes of [n_tokens, W] of the storage dtype, `out_plane` elements apart; mu float32 [n_mix, W];
+// state float32, the row of slot s at state + s * state_ld.
+LLMK_EXPORT int llmk_token_shift_mix(void* out, long long out_plane, const void* x, long long x_ld, const float* mu, float* state,
+                                     long long state_ld, const int* cu_q, const int* state_slots, int n_seqs, int n_tokens, int W,
+                                     int n_mix, int dtype, void* stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return LLMK_OK;
+    if (W <= 0 || n_mix <= 0 || !out || !x || !mu || !state || !cu_q || !state_slots) LLMK_FAIL("token_shift_mix: bad arguments");
+    if (n_tokens > 65535) {
+        // the grid's second dimension counts tokens
+        LLMK_FAIL("token_shift_mix: %d token rows exceed 65535", n_tokens);
+    }
+    dim3 grid(ceil_div(W, 256), n_tokens);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(token_shift_mix_kernel<float>, grid, dim3(256), 0, s, true, (float*)out, out_plane, (const float*)x, x_ld, mu, state,
+                        state_ld, cu_q, state_slots, n_seqs, W, n_mix);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(token_shift_mix_kernel<bf16>, grid, dim3(256), 0, s, true, (bf16*)out, out_plane, (const bf16*)x, x_ld, mu, state,
+                        state_ld, cu_q, state_slots, n_seqs, W, n_mix);
+    else
+        LLMK_FAIL("token_shift_mix: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("token_shift_mix", e);
+    return LLMK_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ decay per key channel
+// Two launches, as for the delta rule.  `decay_prep`, a block per token: q, k, v of the storage dtype go into one float32
+// row [q * q_scale | k | v]; the decays' pre-activations z (float32, [H * D]) become 1 - a, with
+//     mode 0   a = sigmoid(z + b)^(1 / tau)   log a = -softplus(-(z + b)) / tau
+//     mode 1   a = exp(-exp(z + b))           log a = -exp(z + b)
+// and 1 - a = -expm1(log a): a decay just below one keeps its digits only as its distance from one.  Beside them the
+// token's own term, dot[h] = sum_d q_d k_d u_d (u the bonus [H, D], or ones).
+// `decay_scan` has the delta rule's shape (a block per (sequence, head, tile of value columns), SL lanes a column of S,
+// chunks of tokens through shared memory): the token's read-out is q^T S' + dot * v with S' the state after its decay
+// (read after the update: (S' + k v^T)^T q = S'^T q + (q.k) v), or q^T S + dot * v with the state before it.
+enum { DECAY_SIGMOID_POW = 0, DECAY_EXP_EXP = 1 };
+
+template <typename T>
+__global__ void __launch_bounds__(256) decay_prep_kernel(float* __restrict__ qkv, long long qkv_ld, float* __restrict__ decay,
+                                                         float* __restrict__ dots, const T* __restrict__ q, long long q_ld,
+                                                         const T* __restrict__ k, long long k_ld, const T* __restrict__ v,
+                                                         long long v_ld, const float* __restrict__ bias, const float* __restrict__ bonus,
+                                                         int H, int D, int E, int mode, float inv_tau, float q_scale) {
+    const size_t t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
+    float* row = qkv + t * qkv_ld;
+    const int HD = H * D, HE = H * E;
+    for (int head = warp; head < H; head += warps) {
+        float dot = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            const int i = head * D + d;
+            const float qv = to_float(q[t * q_ld + i]) * q_scale, kv = to_float(k[t * k_ld + i]);
+            row[i] = qv;
+            row[HD + i] = kv;
+            dot = fmaf(qv * (bonus ? bonus[i] : 1.f), kv, dot);
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) {
+            dots[t * 2 * H + head] = 1.f;
+            dots[t * 2 * H + H + head] = dot;
+        }
+    }
+    for (int i = threadIdx.x; i < HE; i += blockDim.x) row[2 * HD + i] = to_float(v[t * v_ld + i]);
+    for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+        const float z = decay[t * HD + i] + (bias ? bias[i] : 0.f);
+        const float log_a = mode == DECAY_SIGMOID_POW ? -softplusf_(-z) * inv_tau : -expf(z);
+        decay[t * HD + i] = -expm1f(log_a);
+    }
+}
+
+template <int DSL, int SL, bool READ_FIRST>
+__global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p) {
+    using Sh = DeltaShape<DSL, SL>;
+    constexpr int ROW = Sh::ROW, COLS = Sh::COLS, STRIDE = Sh::STRIDE, BUF = Sh::BUF;
+    extern __shared__ __align__(16) float sm[];
+    const int s = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * COLS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int slice = lane % SL, col = warp * (32 / SL) + lane / SL;
+    const int e = e0 + col;
+    const int D = p.D, E = p.E;
+    // channels beyond key_dim, and value columns beyond value_dim, hold zeros throughout (no decay: 1 - a = 0)
+    for (int i = threadIdx.x; i < 2 * BUF; i += DELTA_THREADS) sm[i] = 0.f;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int q_beg = p.cu_q[s], n = p.cu_q[s + 1] - q_beg;
+    if (n <= 0) return;
+    const int slot = p.state_slots[s];
+    float S[DSL];
+    float* st = slot >= 0 ? p.state + (size_t)slot * p.state_ld + (size_t)h * D * E : nullptr;
+#pragma unroll
+    for (int i = 0; i < DSL; ++i) {
+        const int d = slice * DSL + i;
+        S[i] = (st && d < D && e < E) ? st[(size_t)d * E + e] : 0.f;
+    }
+    __syncthreads();
+    delta_load_chunk<DSL, SL>(p, sm, q_beg, min(DELTA_CHUNK, n), h, h, e0);
+    int turn = 0;
+    for (int c0 = 0; c0 < n; c0 += DELTA_CHUNK, turn ^= 1) {
+        const int nc = min(DELTA_CHUNK, n - c0);
+        cp_async_wait_all();
+        __syncthreads();      // this chunk has arrived, and the chunk before is consumed by every warp
+        if (c0 + DELTA_CHUNK < n)
+            delta_load_chunk<DSL, SL>(p, sm + (turn ^ 1) * BUF, q_beg + c0 + DELTA_CHUNK, min(DELTA_CHUNK, n - c0 - DELTA_CHUNK), h, h, e0);
+        const float* buf = sm + turn * BUF;
+        const float* vs = buf + 3 * DELTA_CHUNK * ROW;
+        const float* bs = vs + DELTA_CHUNK * COLS;
+        auto token = [&](int tt) {
+            const float4* qr = reinterpret_cast<const float4*>(buf + tt * ROW + slice * STRIDE);
+            const float4* kr = reinterpret_cast<const float4*>(buf + DELTA_CHUNK * ROW + tt * ROW + slice * STRIDE);
+            const float4* gr = reinterpret_cast<const float4*>(buf + 2 * DELTA_CHUNK * ROW + tt * ROW + slice * STRIDE);
+            const float val = vs[tt * COLS + col];
+            float qs4[4] = {0.f, 0.f, 0.f, 0.f};      // four sums in turn: short chains of dependent adds
+#pragma unroll
+            for (int i = 0; i < DSL / 4; ++i) {
+                const float4 g4 = gr[i], k4 = kr[i], q4 = qr[i];
+                if (READ_FIRST) {
+                    qs4[0] = fmaf(q4.x, S[4 * i], qs4[0]);
+                    qs4[1] = fmaf(q4.y, S[4 * i + 1], qs4[1]);
+                    qs4[2] = fmaf(q4.z, S[4 * i + 2], qs4[2]);
+                    qs4[3] = fmaf(q4.w, S[4 * i + 3], qs4[3]);
+                }
+                S[4 * i] = fmaf(-g4.x, S[4 * i], S[4 * i]);
+                S[4 * i + 1] = fmaf(-g4.y, S[4 * i + 1], S[4 * i + 1]);
+                S[4 * i + 2] = fmaf(-g4.z, S[4 * i + 2], S[4 * i + 2]);
+                S[4 * i + 3] = fmaf(-g4.w, S[4 * i + 3], S[4 * i + 3]);
+                if (!READ_FIRST) {
+                    qs4[0] = fmaf(q4.x, S[4 * i], qs4[0]);
+                    qs4[1] = fmaf(q4.y, S[4 * i + 1], qs4[1]);
+                    qs4[2] = fmaf(q4.z, S[4 * i + 2], qs4[2]);
+                    qs4[3] = fmaf(q4.w, S[4 * i + 3], qs4[3]);
+                }
+                S[4 * i] = fmaf(k4.x, val, S[4 * i]);
+                S[4 * i + 1] = fmaf(k4.y, val, S[4 * i + 1]);
+                S[4 * i + 2] = fmaf(k4.z, val, S[4 * i + 2]);
+                S[4 * i + 3] = fmaf(k4.w, val, S[4 * i + 3]);
+            }
+            float qS = (qs4[0] + qs4[1]) + (qs4[2] + qs4[3]);
+#pragma unroll
+            for (int o = 1; o < SL; o <<= 1) qS += __shfl_xor_sync(0xffffffffu, qS, o);
+            if (slice == 0 && e < E)
+                p.out[(size_t)(q_beg + c0 + tt) * ((size_t)p.H * E) + (size_t)h * E + e] = fmaf(bs[DELTA_CHUNK + tt], val, qS);
+        };
+        if (nc == DELTA_CHUNK) {
+#pragma unroll
+            for (int tt = 0; tt < DELTA_CHUNK; ++tt) token(tt);
+        } else {
+            for (int tt = 0; tt < nc; ++tt) token(tt);
+        }
+    }
+    if (st) {
+#pragma unroll
+        for (int i = 0; i < DSL; ++i) {
+            const int d = slice * DSL + i;
+            if (d < D && e < E) st[(size_t)d * E + e] = S[i];
+        }
+    }
+}
+
+template <int DSL, int SL>
+static cudaError_t launch_decay(const DeltaParams& p, int n_seqs, bool read_first, cudaStream_t s) {
+    using Sh = DeltaShape<DSL, SL>;
+    const size_t smem = 2 * (size_t)Sh::BUF * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<DSL, SL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(decay_scan_kernel<DSL, SL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    dim3 grid(n_seqs, p.H, ceil_div(p.E, Sh::COLS));
+    if (read_first) return llmk_launch(decay_scan_kernel<DSL, SL, true>, grid, dim3(DELTA_THREADS), smem, s, true, p);
+    return llmk_launch(decay_scan_kernel<DSL, SL, false>, grid, dim3(DELTA_THREADS), smem, s, true, p);
+}
+
+// q, k [n_tokens, H * D] and v [n_tokens, H * E] of the storage dtype (rows q_ld, k_ld, v_ld apart); decay float32
+// [n_tokens, H * D]: the pre-activations, rewritten in place; bias float32 [H * D] or null; bonus float32 [H * D] or null;
+// qkv_buf float32 scratch [n_tokens, 2 H D + H E]; dots float32 scratch [n_tokens, 2 H]; state float32, S [H][D][E] of slot
+// s at state + s * state_ld; out float32 [n_tokens, H * E].  read_first != 0: a token reads the state before its own
+// decay and key enter it (its own key counts `bonus` times); else after both.
+LLMK_EXPORT int llmk_decay_scan(float* out, const void* q, long long q_ld, const void* k, long long k_ld, const void* v, long long v_ld,
+                                float* decay, const float* bias, const float* bonus, float* qkv_buf, float* dots, float* state,
+                                long long state_ld, const int* cu_q, const int* state_slots, int n_seqs, int n_tokens, int H, int D,
+                                int E, int mode, float tau, float q_scale, int read_first, int dtype, void* stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return LLMK_OK;
+    if (H <= 0 || D <= 0 || D > 256 || E <= 0) LLMK_FAIL("decay_scan: heads %d, key width %d (at most 256), value width %d", H, D, E);
+    if (mode != DECAY_SIGMOID_POW && mode != DECAY_EXP_EXP) LLMK_FAIL("decay_scan: unknown decay form %d", mode);
+    if (mode == DECAY_SIGMOID_POW && !(tau > 0.f)) LLMK_FAIL("decay_scan: tau %g must be positive", (double)tau);
+    if (!out || !q || !k || !v || !decay || !qkv_buf || !dots || !state || !cu_q || !state_slots) LLMK_FAIL("decay_scan: bad arguments");
+    if (H > 65535 || ceil_div(E, 8) > 65535) LLMK_FAIL("decay_scan: grid too large");
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long qkv_ld = 2LL * H * D + (long long)H * E;
+    const float inv_tau = mode == DECAY_SIGMOID_POW ? 1.0f / tau : 1.0f;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(decay_prep_kernel<float>, dim3(n_tokens), dim3(256), 0, s, true, qkv_buf, qkv_ld, decay, dots, (const float*)q, q_ld,
+                        (const float*)k, k_ld, (const float*)v, v_ld, bias, bonus, H, D, E, mode, inv_tau, q_scale);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(decay_prep_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, true, qkv_buf, qkv_ld, decay, dots, (const bf16*)q, q_ld,
+                        (const bf16*)k, k_ld, (const bf16*)v, v_ld, bias, bonus, H, D, E, mode, inv_tau, q_scale);
+    else
+        LLMK_FAIL("decay_scan: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("decay_prep", e);
+    DeltaParams p;
+    p.out = out; p.qkv = qkv_buf; p.qkv_ld = qkv_ld; p.beta = dots; p.decay = decay;
+    p.state = state; p.state_ld = state_ld; p.cu_q = cu_q; p.state_slots = state_slots;
+    p.H = H; p.G = H; p.D = D; p.E = E;
+    p.vec_ok = (D % 4 == 0 && E % 4 == 0 && host_aligned16(qkv_buf) && host_aligned16(decay)) ? 1 : 0;
+    const bool rf = read_first != 0;
+    if (D <= 32) e = launch_decay<4, 8>(p, n_seqs, rf, s);
+    else if (D <= 64) e = launch_decay<4, 16>(p, n_seqs, rf, s);
+    else if (D <= 128) e = launch_decay<8, 16>(p, n_seqs, rf, s);
+    else e = launch_decay<16, 16>(p, n_seqs, rf, s);
+    LLMK_CHECK_LAUNCH_RC("decay_scan", e);
     return LLMK_OK;
 }

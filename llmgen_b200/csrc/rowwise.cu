@@ -2,10 +2,15 @@
 // (x <- x + norm(sublayer(x))), and of the sublayers such layers are made of:
 //
 //   norm_add        resid[r, :] += rmsnorm(y[r, :]) * w, and a copy of the new residual row in the storage dtype
-//                   for the products that read the residual itself
+//                   for the products that read the residual itself; y may be a weighted sum of two products
+//                   (a y + b y2), and the copy may be the next sublayer's normed input, rmsnorm(resid) * w_next,
+//                   for layers that norm a sublayer's input as well as its output
+//   scaled_sum      out (float32) = a y + b y2, for consumers that take one array
 //   cast_rows       out = (T) in, float32 in
-//   act_rows        relu(x)^2, or the clamped gated unit  g' s(alpha g') (u' + 1)  with g' = min(g, L), u' = clamp(u, -L, L)
-//   gated_rmsnorm   out[r, :] = rmsnorm(o[r, :]) * w * sigmoid(g[r, :])   (or, without gains, o * sigmoid(g))
+//   act_rows        relu(x)^2, tanh(x), the clamped gated unit  g' s(alpha g') (u' + 1)  with g' = min(g, L), u' = clamp(u, -L, L),
+//                   or the gated units gelu_tanh(g) u and silu(g) u
+//   gated_rmsnorm   out[r, :] = rmsnorm(o[r, :]) * w * sigmoid(g[r, :])   (or, without gains, o * sigmoid(g)); the gate may
+//                   pass silu instead, or enter as it is; the gains may differ between `w_rows` consecutive rows (heads)
 //   add_bias        y[r, :] += b, y an array of T or of float32, or the float32 slices of a product (the first slice takes it)
 //   concat_stream   out[r, :] = [ (T)(resid[r, :] + delta[r, :]) | (T) x0[r, :] ]: the operand of a product that mixes the
 //                   residual stream with the embedding's output
@@ -27,7 +32,9 @@ __device__ __forceinline__ float load_sum(const void* y, size_t at, int splits, 
 
 template <typename T>
 __global__ void norm_add_kernel(float* __restrict__ resid, const void* __restrict__ y, const float* __restrict__ w,
-                                T* __restrict__ copy, int H, float eps, int splits, long long split_stride) {
+                                T* __restrict__ copy, int H, float eps, int splits, long long split_stride,
+                                const void* __restrict__ y2, int splits2, long long split_stride2, float a, float b,
+                                const float* __restrict__ w_next, float eps_next) {
     extern __shared__ float srow[];  // H floats + 33 scratch
     float* scratch = srow + H;
     const size_t r = blockIdx.x;
@@ -35,23 +42,42 @@ __global__ void norm_add_kernel(float* __restrict__ resid, const void* __restric
     pdl_wait();
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = load_sum<T>(y, r * H + i, splits, split_stride);
+        float v = load_sum<T>(y, r * H + i, splits, split_stride);
+        if (y2) v = a * v + b * load_sum<T>(y2, r * H + i, splits2, split_stride2);
         srow[i] = v;
         ss += v * v;
     }
     ss = block_sum(ss, scratch);
     const float rinv = 1.0f / sqrtf(ss / (float)H + eps);
+    if (!w_next) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = resid[r * H + i] + srow[i] * rinv * w[i];
+            resid[r * H + i] = v;
+            if (copy) copy[r * H + i] = from_float<T>(v);
+        }
+        return;
+    }
+    // the copy is the next sublayer's input: the new row normed once more, with the next norm's gains
+    float ss2 = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         const float v = resid[r * H + i] + srow[i] * rinv * w[i];
         resid[r * H + i] = v;
-        if (copy) copy[r * H + i] = from_float<T>(v);
+        srow[i] = v;
+        ss2 += v * v;
     }
+    ss2 = block_sum(ss2, scratch);
+    const float rinv2 = 1.0f / sqrtf(ss2 / (float)H + eps_next);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) copy[r * H + i] = from_float<T>(srow[i] * rinv2 * w_next[i]);
 }
 
-LLMK_EXPORT int llmk_norm_add(float* resid, const void* y, const float* w, void* copy, int n_rows, int H, float eps,
-                              int splits, long long split_stride, int dtype, void* stream) {
+// y2 (with its own slices) null: resid += rmsnorm(y) w.  Else resid += rmsnorm(a y + b y2) w.  w_next non-null: `copy`
+// receives rmsnorm(new row) * w_next (eps_next inside the root) instead of the new row.
+LLMK_EXPORT int llmk_norm_add2(float* resid, const void* y, const float* w, void* copy, int n_rows, int H, float eps,
+                               int splits, long long split_stride, const void* y2, int splits2, long long split_stride2,
+                               float a, float b, const float* w_next, float eps_next, int dtype, void* stream) {
     if (n_rows <= 0) return LLMK_OK;
     if (H <= 0 || !y || !w || !resid) LLMK_FAIL("norm_add: bad arguments (H %d)", H);
+    if (w_next && !copy) LLMK_FAIL("norm_add: the next norm's output needs a place");
     const size_t smem = ((size_t)H + 33) * sizeof(float);
     if (smem > 200 * 1024) LLMK_FAIL("norm_add: a row of %d values does not fit shared memory", H);
     const int threads = H >= 2048 ? 512 : H >= 512 ? 256 : 128;
@@ -59,13 +85,48 @@ LLMK_EXPORT int llmk_norm_add(float* resid, const void* y, const float* w, void*
     cudaError_t e;
     if (dtype == LLMK_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = llmk_launch(norm_add_kernel<float>, dim3(n_rows), dim3(threads), smem, s, true, resid, y, w, (float*)copy, H, eps, splits, split_stride);
+        e = llmk_launch(norm_add_kernel<float>, dim3(n_rows), dim3(threads), smem, s, true, resid, y, w, (float*)copy, H, eps, splits, split_stride,
+                        y2, splits2, split_stride2, a, b, w_next, eps_next);
     } else if (dtype == LLMK_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = llmk_launch(norm_add_kernel<bf16>, dim3(n_rows), dim3(threads), smem, s, true, resid, y, w, (bf16*)copy, H, eps, splits, split_stride);
+        e = llmk_launch(norm_add_kernel<bf16>, dim3(n_rows), dim3(threads), smem, s, true, resid, y, w, (bf16*)copy, H, eps, splits, split_stride,
+                        y2, splits2, split_stride2, a, b, w_next, eps_next);
     } else
         LLMK_FAIL("norm_add: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("norm_add", e);
+    return LLMK_OK;
+}
+
+LLMK_EXPORT int llmk_norm_add(float* resid, const void* y, const float* w, void* copy, int n_rows, int H, float eps,
+                              int splits, long long split_stride, int dtype, void* stream) {
+    return llmk_norm_add2(resid, y, w, copy, n_rows, H, eps, splits, split_stride, nullptr, 0, 0, 1.f, 0.f, nullptr, 0.f, dtype, stream);
+}
+
+// out[i] (float32) = a * y[i] + b * y2[i]; y and y2 arrays of T or float32 slices.
+template <typename T>
+__global__ void scaled_sum_kernel(float* __restrict__ out, const void* __restrict__ y, int splits, long long split_stride,
+                                  const void* __restrict__ y2, int splits2, long long split_stride2, float a, float b, long long n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = a * load_sum<T>(y, (size_t)i, splits, split_stride) + b * load_sum<T>(y2, (size_t)i, splits2, split_stride2);
+}
+
+LLMK_EXPORT int llmk_scaled_sum(float* out, const void* y, int splits, long long split_stride, const void* y2, int splits2,
+                                long long split_stride2, float a, float b, long long n, int dtype, void* stream) {
+    if (n <= 0) return LLMK_OK;
+    if (!out || !y || !y2) LLMK_FAIL("scaled_sum: bad arguments");
+    long long blocks = (n + 255) / 256;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(scaled_sum_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, out, y, splits, split_stride, y2, splits2, split_stride2, a, b, n);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(scaled_sum_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, true, out, y, splits, split_stride, y2, splits2, split_stride2, a, b, n);
+    else
+        LLMK_FAIL("scaled_sum: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("scaled_sum", e);
     return LLMK_OK;
 }
 
@@ -97,7 +158,9 @@ LLMK_EXPORT int llmk_cast_rows(void* out, const float* in, long long n, int dtyp
 // mode 1: x [n, 2F], gate in columns [0, F), up in [F, 2F):
 //         g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1)
 // mode 2: x [n, 2F] as in mode 1: out = gelu_tanh(gate) * up, gelu_tanh(z) = z / 2 (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
-enum { ACT_RELU2 = 0, ACT_CLAMPED_GLU = 1, ACT_GELU_TANH_GLU = 2 };
+// mode 3: out[r, f] = tanh(x[r, f]), x [n, F]
+// mode 4: x [n, 2F] as in mode 2 (groups too): out = silu(gate) * up
+enum { ACT_RELU2 = 0, ACT_CLAMPED_GLU = 1, ACT_GELU_TANH_GLU = 2, ACT_TANH = 3, ACT_SILU_GLU = 4 };
 
 __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -116,10 +179,13 @@ __global__ void act_rows_kernel(T* __restrict__ out, const void* __restrict__ x,
         if (mode == ACT_RELU2) {
             const float a = fmaxf(load_sum<T>(x, r * ld + f, splits, split_stride), 0.f);
             v = a * a;
-        } else if (mode == ACT_GELU_TANH_GLU) {
+        } else if (mode == ACT_TANH) {
+            v = tanhf(load_sum<T>(x, r * ld + f, splits, split_stride));
+        } else if (mode == ACT_GELU_TANH_GLU || mode == ACT_SILU_GLU) {
             // gate and up alternate in groups of `group` columns (group = F: all gates, then all ups)
             const size_t gc = r * ld + (size_t)(f / group) * 2 * group + f % group;
-            v = gelu_tanh(load_sum<T>(x, gc, splits, split_stride)) * load_sum<T>(x, gc + group, splits, split_stride);
+            const float g = load_sum<T>(x, gc, splits, split_stride);
+            v = (mode == ACT_SILU_GLU ? g / (1.0f + expf(-g)) : gelu_tanh(g)) * load_sum<T>(x, gc + group, splits, split_stride);
         } else {
             const float g = fminf(load_sum<T>(x, r * ld + f, splits, split_stride), limit);
             const float u = fminf(fmaxf(load_sum<T>(x, r * ld + F + f, splits, split_stride), -limit), limit);
@@ -134,7 +200,7 @@ LLMK_EXPORT int llmk_act_rows(void* out, const void* x, int n, int F, long long 
     if (n <= 0 || F <= 0) return LLMK_OK;
     if (group <= 0) group = F;
     if (F % group != 0) LLMK_FAIL("act_rows: groups of %d columns do not divide %d", group, F);
-    if (mode != ACT_RELU2 && mode != ACT_CLAMPED_GLU && mode != ACT_GELU_TANH_GLU) LLMK_FAIL("act_rows: unknown activation %d", mode);
+    if (mode < ACT_RELU2 || mode > ACT_SILU_GLU) LLMK_FAIL("act_rows: unknown activation %d", mode);
     long long blocks = ((long long)n * F + 255) / 256;
     if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
     cudaStream_t s = (cudaStream_t)stream;
@@ -149,11 +215,15 @@ LLMK_EXPORT int llmk_act_rows(void* out, const void* x, int n, int F, long long 
     return LLMK_OK;
 }
 
-// out[r, i] = o[r, i] * (w ? rsqrt(mean(o[r, :]^2) + eps) * w[i] : 1) * sigmoid(g[r, i]); o float32 [n, H], g of T with rows
-// `ldg` apart.
+// out[r, i] = o[r, i] * (w ? rsqrt(mean(o[r, :]^2) + eps) * w[i] : 1) * gate(g[r, i]); o float32 [n, H], g of T with rows `ldg`
+// apart.  gate_act 0: sigmoid(g); 1: silu(g); 2: g as it is.  heads > 1: a row is one head of a token, r = token * heads +
+// head; the gate's rows are tokens ([n / heads, heads * H], `ldg` apart), and with w_rows = heads every head has gains of
+// its own, w [heads, H] (w_rows = 1: one vector for all).
+enum { GATE_SIGMOID = 0, GATE_SILU = 1, GATE_PLAIN = 2 };
 template <typename T>
 __global__ void gated_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ g,
-                                     const float* __restrict__ w, int H, long long ldg, float eps) {
+                                     const float* __restrict__ w, int H, long long ldg, float eps, int gate_act, int w_rows,
+                                     int heads) {
     __shared__ float scratch[33];
     const size_t r = blockIdx.x;
     pdl_launch_dependents();
@@ -168,22 +238,29 @@ __global__ void gated_rmsnorm_kernel(T* __restrict__ out, const float* __restric
         ss = block_sum(ss, scratch);
         rinv = 1.0f / sqrtf(ss / (float)H + eps);
     }
+    const size_t head = r % (size_t)heads;
+    const float* wr = w ? w + (head % (size_t)w_rows) * H : nullptr;
+    const T* gr = g + (r / (size_t)heads) * ldg + head * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float gate = 1.0f / (1.0f + expf(-to_float(g[r * ldg + i])));
-        out[r * H + i] = from_float<T>(o[r * H + i] * rinv * (w ? w[i] : 1.f) * gate);
+        const float gv = to_float(gr[i]);
+        const float sg = 1.0f / (1.0f + expf(-gv));
+        const float gate = gate_act == GATE_SIGMOID ? sg : gate_act == GATE_SILU ? gv * sg : gv;
+        out[r * H + i] = from_float<T>(o[r * H + i] * rinv * (wr ? wr[i] : 1.f) * gate);
     }
 }
 
 LLMK_EXPORT int llmk_gated_rmsnorm(void* out, const float* o, const void* g, const float* w, int n_rows, int H, long long ldg,
-                                   float eps, int dtype, void* stream) {
+                                   float eps, int gate_act, int w_rows, int heads, int dtype, void* stream) {
     if (n_rows <= 0 || H <= 0) return LLMK_OK;
+    if (gate_act < GATE_SIGMOID || gate_act > GATE_PLAIN || heads < 1 || (w_rows != 1 && w_rows != heads))
+        LLMK_FAIL("gated_rmsnorm: gate form %d, %d heads a token, %d rows of gains", gate_act, heads, w_rows);
     const int threads = H >= 2048 ? 512 : H >= 512 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
     if (dtype == LLMK_F32)
-        e = llmk_launch(gated_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, true, (float*)out, o, (const float*)g, w, H, ldg, eps);
+        e = llmk_launch(gated_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, true, (float*)out, o, (const float*)g, w, H, ldg, eps, gate_act, w_rows, heads);
     else if (dtype == LLMK_BF16)
-        e = llmk_launch(gated_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, true, (bf16*)out, o, (const bf16*)g, w, H, ldg, eps);
+        e = llmk_launch(gated_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, true, (bf16*)out, o, (const bf16*)g, w, H, ldg, eps, gate_act, w_rows, heads);
     else
         LLMK_FAIL("gated_rmsnorm: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("gated_rmsnorm", e);

@@ -42,6 +42,7 @@ class DecoderModel:
             if item.before is not None and item.before not in made:
                 made[item.before] = Reentry(item.before, weights, dtype, device)
             self.before.append(made.get(item.before))
+        self.embedding_norm = build_norm(spec.embedding_norm, weights, dtype, device) if spec.embedding_norm is not None else None
         self.final_norm = build_norm(spec.final_norm, weights, dtype, device)
         self.lm_head = weights.device_tensor(spec.lm_head, dtype, device)   # the embedding itself when tied
         weights.release()
@@ -88,19 +89,28 @@ class DecoderModel:
         """Run embedding and all run items; returns (residual float32 [T, H], pending delta)."""
         T, H = ctx.n_tokens, self.spec.hidden_size
         resid = ctx.workspace.buffer("residual", T, H, torch.float32)
-        ops.embed_rows(resid, self.embedding, ctx.ids, self.bad_token_flag, ids_from=ctx.ids_from, sampled=ctx.prev_sampled,
+        rows = resid if self.embedding_norm is None else ctx.workspace.buffer("embedding_rows", T, H, torch.float32)
+        ops.embed_rows(rows, self.embedding, ctx.ids, self.bad_token_flag, ids_from=ctx.ids_from, sampled=ctx.prev_sampled,
                        scale=float(self.spec.embedding_scale))
+        if self.embedding_norm is not None:
+            # the table's rows pass a norm before they become the residual stream (float32 in, float32 out)
+            self.embedding_norm.add_norm(rows, None, resid)
         x0 = None
         if any(b is not None for b in self.before):
             # the embedding's output, for the run items that mix it back into the stream
             x0 = ctx.workspace.buffer("embedding_out", T, H, torch.float32)
             ops.widen(x0, resid)
         delta = None
-        for item, cache, before in zip(self.spec.run_order, caches, self.before):
+        ctx.normed_for = None
+        order = self.spec.run_order
+        for n, (item, cache, before) in enumerate(zip(order, caches, self.before)):
             if before is not None:
                 before.forward(ctx, resid, delta, x0)
                 delta = None
+            # blocks that prepare the next block's input are told which block that is (none behind a re-entry step)
+            ctx.next_block = (self.layers[order[n + 1].layer] if n + 1 < len(order) and self.before[n + 1] is None else None)
             delta = self.layers[item.layer].forward(ctx, resid, delta, cache)
+        ctx.next_block = None
         return resid, delta
 
     def logits(self, ctx: StepContext, resid: torch.Tensor, delta: Optional[torch.Tensor],

@@ -165,9 +165,11 @@ def widen(out: torch.Tensor, src: torch.Tensor) -> None:
 # ------------------------------------------------------------------------------ attn_prep
 # Codes of the C ABI (csrc/common.cuh).  "half": pairs (i, i + rot / 2), the reference's pairing
 # (src/backend/cpu/rope.zig:13-45); "interleaved": pairs (2i, 2i + 1).  The latent-attention kernels implement both; the
-# grouped-query attention kernels implement "half" and refuse the other with a message, never rotate wrongly.
+# grouped-query attention's preparation kernel implements both in its general form ("half" alone in the 16-byte forms
+# and inside the decode kernel); what a kernel does not implement it refuses with a message, never rotates wrongly.
 ROTARY_PAIRINGS = {"half": 0, "interleaved": 1}
-HEAD_NORMS = {"rmsnorm": 0}
+# "rmsnorm": gains, before the rotation; "unit_rms_after": no gains, over the rotated head
+HEAD_NORMS = {"rmsnorm": 0, "unit_rms_after": 1}
 
 
 def pairing_code(pairing: str) -> int:
@@ -536,10 +538,11 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: t
                     tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, n_tokens: int, nq: int, nkv: int,
                     hd: int, page_size: int, window: int, scale: float, num_parts: int = 1, part_size: int = 0,
                     scratch: Optional[torch.Tensor] = None, vd: int = 0, softcap: float = 0.0, sink: bool = False,
-                    gate: Optional[torch.Tensor] = None) -> None:
+                    gate: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
     """out[t, nq*vd] = causal GQA of q[t] over the paged cache (see csrc/attention.cu).  `vd`: the values' width where
     it differs from `hd`; `softcap` > 0 bounds the scores by softcap * tanh(s / softcap); `sink` adds exp(0) to the
-    softmax's denominator; `gate` [tokens, nq*vd] (storage dtype): the result is multiplied by sigmoid(gate)."""
+    softmax's denominator; `gate` [tokens, nq*vd] (storage dtype): the result is multiplied by sigmoid(gate); `chunk` > 0:
+    a query sees the keys at or before it inside its own block of that many positions, counted from the sequence's start."""
     lib = build.load("attention")
     if gate is not None and gate.dtype != q.dtype:
         raise KernelError("paged_attention: the gate has the storage dtype")
@@ -553,7 +556,7 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: t
                                          c_int(n_tokens), c_int(nq), c_int(nkv), c_int(hd), c_int(page_size),
                                          c_int(window), c_float(scale), c_int(num_parts), c_int(part_size),
                                          _ptr(scratch), c_int(vd), c_float(softcap), c_int(1 if sink else 0), _ptr(gate),
-                                         c_longlong(_row_stride(gate) if gate is not None else 0),
+                                         c_longlong(_row_stride(gate) if gate is not None else 0), c_int(chunk),
                                          c_int(dtype_code(q.dtype)), _stream()),
            2 if num_parts > 1 else 1)
 
@@ -566,7 +569,7 @@ def attention_mma_tile_queries(nq: int, nkv: int, hd: int, vd: int) -> int:
 def attention_mma(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
                   max_blocks: int, ctx_len: torch.Tensor, cu_q: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor,
                   n_tiles: int, nq: int, nkv: int, hd: int, vd: int, page_size: int, window: int, scale: float,
-                  softcap: float = 0.0, sink: bool = False, gate: Optional[torch.Tensor] = None) -> None:
+                  softcap: float = 0.0, sink: bool = False, gate: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
     """Prompt portions in bfloat16 with 32-bit softmax weights on the tensor cores (csrc/attention_mma.cu): the same
     result as `paged_attention` with these options, tiles of `attention_mma_tile_queries` queries."""
     lib = build.load("attention_mma")
@@ -576,7 +579,7 @@ def attention_mma(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcac
                                        _ptr(vcache), _ptr(block_tables), c_int(max_blocks), _ptr(ctx_len), _ptr(cu_q), _ptr(tile_seq),
                                        _ptr(tile_q0), c_int(n_tiles), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), c_int(page_size),
                                        c_int(window), c_float(scale), c_float(softcap), c_int(1 if sink else 0), _ptr(gate),
-                                       c_longlong(_row_stride(gate) if gate is not None else 0), _stream()))
+                                       c_longlong(_row_stride(gate) if gate is not None else 0), c_int(chunk), _stream()))
 
 
 def attention_decode_set_cluster_merge(on: bool) -> None:
@@ -700,7 +703,7 @@ def sample(out_ids: torch.Tensor, logits: torch.Tensor, temps: torch.Tensor, see
 
 
 # ---------------------------------------------------------------------- rows of post-norm layers
-ACTIVATIONS = {"relu2": 0, "clamped_glu": 1, "gelu_tanh_glu": 2}
+ACTIVATIONS = {"relu2": 0, "clamped_glu": 1, "gelu_tanh_glu": 2, "tanh": 3, "silu_glu": 4}
 
 
 def _delta_args(y, dtype: torch.dtype):
@@ -712,19 +715,59 @@ def _delta_args(y, dtype: torch.dtype):
     return y, 0, 0
 
 
-def norm_add(resid: torch.Tensor, y, weight: torch.Tensor, eps: float, copy: Optional[torch.Tensor], dtype: torch.dtype) -> None:
-    """resid (float32 [n, H]) += rmsnorm(y) * weight; `copy` (storage dtype [n, H], or None) receives the new rows.
-    `y` is an array of the storage dtype or a `Partials`."""
+def norm_add(resid: torch.Tensor, y, weight: torch.Tensor, eps: float, copy: Optional[torch.Tensor], dtype: torch.dtype,
+             next_gain: Optional[torch.Tensor] = None, next_eps: float = 0.0) -> None:
+    """resid (float32 [n, H]) += rmsnorm(y) * weight; `copy` (storage dtype [n, H], or None) receives the new rows, or,
+    with `next_gain`, rmsnorm(new rows) * next_gain: the input of a sublayer that norms what it reads.
+    `y` is an array of the storage dtype, a `Partials`, or a `WeightedPair` of two such (a y1 + b y2)."""
     lib = build.load("rowwise")
     n, H = resid.shape
-    if resid.dtype != torch.float32 or weight.dtype != torch.float32:
-        raise KernelError("norm_add: residual and gain must be float32")
+    if resid.dtype != torch.float32 or weight.dtype != torch.float32 or (next_gain is not None and next_gain.dtype != torch.float32):
+        raise KernelError("norm_add: residual and gains must be float32")
+    second, a, b = None, 1.0, 0.0
+    if isinstance(y, WeightedPair):
+        y, second, a, b = y.first, y.second, y.a, y.b
     src, splits, stride = _delta_args(y, dtype)
+    src2, splits2, stride2 = _delta_args(second, dtype) if second is not None else (None, 0, 0)
     rows = y.rows if isinstance(y, Partials) else y.shape[0]
     if rows != n or (copy is not None and (copy.dtype != dtype or tuple(copy.shape) != (n, H) or not copy.is_contiguous())):
         raise KernelError("norm_add: shapes do not fit")
-    _check(lib, lib.llmk_norm_add(_ptr(resid), _ptr(src), _ptr(weight), _ptr(copy), c_int(n), c_int(H), c_float(eps),
-                                  c_int(splits), c_longlong(stride), c_int(dtype_code(dtype)), _stream()))
+    if next_gain is not None and copy is None:
+        raise KernelError("norm_add: the next norm's output needs a place")
+    _check(lib, lib.llmk_norm_add2(_ptr(resid), _ptr(src), _ptr(weight), _ptr(copy), c_int(n), c_int(H), c_float(eps),
+                                   c_int(splits), c_longlong(stride), _ptr(src2), c_int(splits2), c_longlong(stride2), c_float(a),
+                                   c_float(b), _ptr(next_gain), c_float(next_eps), c_int(dtype_code(dtype)), _stream()))
+
+
+class WeightedPair:
+    """a * first + b * second, not yet added up: what a mixer made of two mixers side by side returns.  Each of the two
+    is an array of the storage dtype or a `Partials`.  `norm_add` takes it as it is; `scaled_sum` adds it up for
+    consumers that take one array."""
+
+    def __init__(self, first, a: float, second, b: float):
+        self.first, self.a, self.second, self.b = first, float(a), second, float(b)
+
+    @property
+    def rows(self) -> int:
+        return self.first.rows if isinstance(self.first, Partials) else self.first.shape[0]
+
+    @property
+    def cols(self) -> int:
+        return self.first.cols if isinstance(self.first, Partials) else self.first.shape[1]
+
+
+def scaled_sum(out: torch.Tensor, pair: WeightedPair, dtype: torch.dtype) -> Partials:
+    """out (float32 [1, n, H], contiguous) = a * first + b * second; returned as a one-slice `Partials`."""
+    lib = build.load("rowwise")
+    if out.dtype != torch.float32 or not out.is_contiguous() or out.dim() != 3 or out.shape[0] != 1 or out.shape[1] != pair.rows \
+            or out.shape[2] != pair.cols:
+        raise KernelError("scaled_sum: the sum goes to a contiguous float32 [1, rows, cols] array")
+    src, splits, stride = _delta_args(pair.first, dtype)
+    src2, splits2, stride2 = _delta_args(pair.second, dtype)
+    _check(lib, lib.llmk_scaled_sum(_ptr(out), _ptr(src), c_int(splits), c_longlong(stride), _ptr(src2), c_int(splits2),
+                                    c_longlong(stride2), c_float(pair.a), c_float(pair.b), c_longlong(pair.rows * pair.cols),
+                                    c_int(dtype_code(dtype)), _stream()))
+    return Partials(out)
 
 
 def cast_rows(out: torch.Tensor, src: torch.Tensor) -> None:
@@ -738,8 +781,9 @@ def cast_rows(out: torch.Tensor, src: torch.Tensor) -> None:
 def act_rows(out: torch.Tensor, x, activation: str, alpha: float = 1.0, limit: float = 0.0, group: int = 0) -> None:
     """out[n, F] = relu(x)^2 ("relu2", x [n, F]) or the clamped gated unit of x [n, 2F] ("clamped_glu": gate in
     the first F columns, up in the last): g' = min(g, limit), u' = clamp(u, -limit, limit),
-    out = g' sigmoid(alpha g') (u' + 1); or gelu_tanh(gate) * up of x [n, 2F] ("gelu_tanh_glu", where `group` > 0 says
-    that gate and up columns alternate in groups of that many).  `x` is an array or a `Partials`."""
+    out = g' sigmoid(alpha g') (u' + 1); or gelu_tanh(gate) * up / silu(gate) * up of x [n, 2F] ("gelu_tanh_glu", "silu_glu",
+    where `group` > 0 says that gate and up columns alternate in groups of that many); or tanh(x) ("tanh", x [n, F]).
+    `x` is an array or a `Partials`."""
     lib = build.load("rowwise")
     try:
         mode = ACTIVATIONS[activation]
@@ -756,15 +800,28 @@ def act_rows(out: torch.Tensor, x, activation: str, alpha: float = 1.0, limit: f
                                   c_int(splits), c_longlong(stride), c_int(group), c_int(dtype_code(out.dtype)), _stream()))
 
 
-def gated_rmsnorm(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], eps: float) -> None:
-    """out[n, H] (storage dtype) = rmsnorm(o) * weight * sigmoid(gate); o float32 [n, H] contiguous, gate of the storage
-    dtype with any row stride.  Without `weight`: o * sigmoid(gate)."""
+GATE_FORMS = {"sigmoid": 0, "silu": 1, "plain": 2}
+
+
+def gated_rmsnorm(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], eps: float,
+                  gate_form: str = "sigmoid", heads: int = 1, gains_per_head: bool = False) -> None:
+    """out[n, H] (storage dtype) = rmsnorm(o) * weight * f(gate), f the sigmoid, silu, or the gate as it is (`gate_form`);
+    o float32 [n, H] contiguous, gate of the storage dtype with any row stride.  Without `weight`: o * f(gate).
+    `heads` > 1: every row of out and o is one head of a token (row = token * heads + head) and the gate is
+    [n / heads, heads * H] with any row stride; `weight` is then [H], shared by the heads, or, with `gains_per_head`,
+    [heads, H]."""
     lib = build.load("rowwise")
     n, H = out.shape
-    if o.dtype != torch.float32 or not o.is_contiguous() or gate.dtype != out.dtype:
+    if o.dtype != torch.float32 or not o.is_contiguous() or gate.dtype != out.dtype or n % heads != 0:
         raise KernelError("gated_rmsnorm: o must be contiguous float32 and the gate of the storage dtype")
+    w_rows = heads if gains_per_head else 1
+    if weight is not None and (weight.dtype != torch.float32 or weight.numel() != w_rows * H or not weight.is_contiguous()):
+        raise KernelError("gated_rmsnorm: the gains are float32 [H] or [heads, H]")
+    if tuple(gate.shape) != (n // heads, heads * H):
+        raise KernelError("gated_rmsnorm: the gate is [tokens, heads * H]")
     _check(lib, lib.llmk_gated_rmsnorm(_ptr(out), _ptr(o), _ptr(gate), _ptr(weight), c_int(n), c_int(H), c_longlong(_row_stride(gate)),
-                                       c_float(eps), c_int(dtype_code(out.dtype)), _stream()))
+                                       c_float(eps), c_int(GATE_FORMS[gate_form]), c_int(w_rows), c_int(heads),
+                                       c_int(dtype_code(out.dtype)), _stream()))
 
 
 def add_bias(y, bias: torch.Tensor) -> None:
@@ -870,6 +927,52 @@ def delta_scan(out: torch.Tensor, qkv: torch.Tensor, beta: torch.Tensor, decay: 
                                     _ptr(decay), _ptr(beta_buf), _ptr(dt_bias), _ptr(a_log), _ptr(state), c_longlong(_row_stride(state)),
                                     _ptr(cu_q), _ptr(state_slots), c_int(n_seqs), c_int(n), c_int(heads), c_int(kv_heads), c_int(dim),
                                     c_int(vdim), c_float(unit_eps), c_float(q_scale), c_int(dtype_code(beta.dtype)), _stream()), 2)
+
+
+DECAY_FORMS = {"sigmoid_pow": 0, "exp_exp": 1}
+
+
+def token_shift_mix(out: torch.Tensor, x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor,
+                    state_slots: torch.Tensor, n_seqs: int) -> None:
+    """out[i, t] = x[t] + (x[t - 1] - x[t]) * mu[i] for every blend i (csrc/recurrent.cu): out [n_mix, n, W] of the storage
+    dtype, x [n, W], mu float32 [n_mix, W].  A sequence's first token of the step reads its state row (float32 [slots, >= W],
+    zeros for a fresh request) as the token before it, and the sequence's last row is left there."""
+    lib = build.load("recurrent")
+    n_mix, n, W = out.shape
+    if x.dtype != out.dtype or tuple(x.shape) != (n, W) or not out.is_contiguous() or mu.dtype != torch.float32 or tuple(mu.shape) != (n_mix, W) \
+            or not mu.is_contiguous() or state.dtype != torch.float32 or state.shape[1] < W:
+        raise KernelError("token_shift_mix: shapes or dtypes do not fit")
+    _check(lib, lib.llmk_token_shift_mix(_ptr(out), c_longlong(n * W), _ptr(x), c_longlong(_row_stride(x)), _ptr(mu), _ptr(state),
+                                         c_longlong(_row_stride(state)), _ptr(cu_q), _ptr(state_slots), c_int(n_seqs), c_int(n), c_int(W),
+                                         c_int(n_mix), c_int(dtype_code(x.dtype)), _stream()))
+
+
+def decay_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, bias: Optional[torch.Tensor],
+               bonus: Optional[torch.Tensor], state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int, heads: int,
+               dim: int, vdim: int, form: str, tau: float, q_scale: float, read_first: bool, qkv_buf: torch.Tensor, dots: torch.Tensor) -> None:
+    """Linear attention with a decay per head and key channel over each sequence's new tokens (csrc/recurrent.cu).
+    q, k [n, heads dim], v [n, heads vdim] of the storage dtype (any row stride); decay float32 [n, heads dim], the decays'
+    pre-activations z, REWRITTEN; with b = `bias` (float32 [heads dim]) the decay is sigmoid(z + b)^(1/tau) ("sigmoid_pow")
+    or exp(-exp(z + b)) ("exp_exp").  state float32 [slots, >= heads dim vdim]; out float32 [n, heads vdim].
+    `read_first`: o = (S + diag(bonus) k v^T)^T q before S <- diag(a) S + k v^T; else o = S^T q after it.  q is multiplied
+    by `q_scale`.  `qkv_buf` float32 scratch [n, 2 heads dim + heads vdim], `dots` float32 scratch [n, 2 heads]."""
+    lib = build.load("recurrent")
+    n = out.shape[0]
+    if any(t.dtype != torch.float32 for t in (out, decay, state, qkv_buf, dots)) or q.dtype != k.dtype or q.dtype != v.dtype:
+        raise KernelError("decay_scan: out, decay, state and the scratch are float32; q, k, v share the storage dtype")
+    if not out.is_contiguous() or not decay.is_contiguous() or out.shape[1] != heads * vdim or decay.shape[1] != heads * dim \
+            or q.shape[1] != heads * dim or k.shape[1] != heads * dim or v.shape[1] != heads * vdim or state.shape[1] < heads * dim * vdim \
+            or qkv_buf.numel() < n * (2 * heads * dim + heads * vdim) or dots.numel() < 2 * n * heads or not qkv_buf.is_contiguous() \
+            or not dots.is_contiguous():
+        raise KernelError("decay_scan: shapes do not fit")
+    for name, t in (("bias", bias), ("bonus", bonus)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != heads * dim or not t.is_contiguous()):
+            raise KernelError(f"decay_scan: {name} is float32 [heads, dim]")
+    _check(lib, lib.llmk_decay_scan(_ptr(out), _ptr(q), c_longlong(_row_stride(q)), _ptr(k), c_longlong(_row_stride(k)), _ptr(v),
+                                    c_longlong(_row_stride(v)), _ptr(decay), _ptr(bias), _ptr(bonus), _ptr(qkv_buf), _ptr(dots), _ptr(state),
+                                    c_longlong(_row_stride(state)), _ptr(cu_q), _ptr(state_slots), c_int(n_seqs), c_int(n), c_int(heads),
+                                    c_int(dim), c_int(vdim), c_int(DECAY_FORMS[form]), c_float(tau), c_float(q_scale),
+                                    c_int(1 if read_first else 0), c_int(dtype_code(q.dtype)), _stream()), 2)
 
 
 # ------------------------------------------------------------------------------ linear attention
@@ -1010,7 +1113,8 @@ def latent_expand(out: torch.Tensor, oa: torch.Tensor, wuv: torch.Tensor, gate: 
 
 
 # -------------------------------------------------------------------------- routed feed-forward
-ROUTER_SCORINGS = {"sigmoid": 0, "softmax": 1}
+# "softmax_top": the logits choose, the weights are the softmax over the chosen logits alone
+ROUTER_SCORINGS = {"sigmoid": 0, "softmax": 1, "softmax_top": 2}
 
 
 MOE_GROUPED_TILE = 128      # rows per tile of the grouped tensor-core product
@@ -1022,15 +1126,16 @@ def moe_max_tiles(n_slots: int, experts: int, tile: int = 0) -> int:
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, slot_expert: torch.Tensor, slot_weight: torch.Tensor, top: int,
-              scoring: str = "sigmoid", renormalize: bool = False) -> None:
-    """Per row of h [n, K]: scores of router (float32 [E, K]) h, the `top` largest choose; slot n * top + c receives
-    (expert, score)."""
+              scoring: str = "sigmoid", renormalize: bool = False, bias: Optional[torch.Tensor] = None) -> None:
+    """Per row of h [n, K]: scores of router (float32 [E, K]) h (+ `bias`, float32 [E]), the `top` largest choose; slot
+    n * top + c receives (expert, score)."""
     lib = build.load("moe")
     n, K = h.shape
     E = router.shape[0]
-    if router.dtype != torch.float32 or slot_expert.dtype != torch.int32 or slot_weight.dtype != torch.float32:
-        raise KernelError("moe_route: router and weights float32, experts int32")
-    _check(lib, lib.llmk_moe_route(_ptr(h), c_longlong(_row_stride(h)), _ptr(router), _ptr(slot_expert), _ptr(slot_weight), c_int(n),
+    if router.dtype != torch.float32 or slot_expert.dtype != torch.int32 or slot_weight.dtype != torch.float32 \
+            or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != E)):
+        raise KernelError("moe_route: router, bias and weights float32, experts int32")
+    _check(lib, lib.llmk_moe_route(_ptr(h), c_longlong(_row_stride(h)), _ptr(router), _ptr(bias), _ptr(slot_expert), _ptr(slot_weight), c_int(n),
                                    c_int(K), c_int(E), c_int(top), c_int(ROUTER_SCORINGS[scoring]), c_int(1 if renormalize else 0),
                                    c_int(dtype_code(h.dtype)), _stream()))
 
@@ -1075,8 +1180,10 @@ def gemm_tc_grouped(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, tile_gr
 
 def moe_experts(out: torch.Tensor, x: torch.Tensor, w0: torch.Tensor, w1: Optional[torch.Tensor], order: torch.Tensor,
                 slot_weight: torch.Tensor, tile_expert: torch.Tensor, tile_start: torch.Tensor, tile_rows: torch.Tensor,
-                n_slots: int, top: int, first: bool, weight_on_input: bool, alpha: float = 1.0, limit: float = 0.0) -> None:
-    """first: out float32 [slots, ff] = gated activation of the rows' products with w0 = gate, w1 = up [E, ff, K];
+                n_slots: int, top: int, first: bool, weight_on_input: bool, alpha: float = 1.0, limit: float = 0.0,
+                plain: bool = False) -> None:
+    """first: out float32 [slots, ff] = gated activation of the rows' products with w0 = gate, w1 = up [E, ff, K]
+    (`plain`: silu(gate) * up instead of the clamped unit);
     else out float32 [slots, K] = rows of x (float32 [slots, ff]) times w0 = down [E, K, ff]."""
     lib = build.load("moe")
     E, N, K = w0.shape
@@ -1085,13 +1192,15 @@ def moe_experts(out: torch.Tensor, x: torch.Tensor, w0: torch.Tensor, w1: Option
     _check(lib, lib.llmk_moe_experts(_ptr(out), _ptr(x), c_longlong(_row_stride(x)), _ptr(w0), _ptr(w1), _ptr(order), _ptr(slot_weight),
                                      _ptr(tile_expert), _ptr(tile_start), _ptr(tile_rows), c_int(n_slots), c_int(E), c_int(top),
                                      c_int(K), c_int(N), c_int(1 if first else 0), c_int(1 if weight_on_input else 0), c_float(alpha),
-                                     c_float(limit), c_int(dtype_code(w0.dtype)), _stream()))
+                                     c_float(limit), c_int(1 if plain else 0), c_int(dtype_code(w0.dtype)), _stream()))
 
 
-def moe_combine(out: torch.Tensor, rows: torch.Tensor, pos_of_slot: torch.Tensor, shared_out: Optional[torch.Tensor], top: int) -> None:
-    """out float32 [n, H] = shared_out (storage dtype, or None) + the token's `top` rows of `rows` (float32 [slots, H])."""
+def moe_combine(out: torch.Tensor, rows: torch.Tensor, pos_of_slot: torch.Tensor, shared_out: Optional[torch.Tensor], top: int,
+                slot_weight: Optional[torch.Tensor] = None) -> None:
+    """out float32 [n, H] = shared_out (storage dtype, or None) + the token's `top` rows of `rows` (float32 [slots, H]), each
+    times its slot's weight where `slot_weight` (float32 [n * top]) is given."""
     lib = build.load("moe")
     n, H = out.shape
     dt = shared_out.dtype if shared_out is not None else torch.float32
-    _check(lib, lib.llmk_moe_combine(_ptr(out), _ptr(rows), _ptr(pos_of_slot), _ptr(shared_out), c_int(n), c_int(top), c_int(H),
+    _check(lib, lib.llmk_moe_combine(_ptr(out), _ptr(rows), _ptr(pos_of_slot), _ptr(shared_out), _ptr(slot_weight), c_int(n), c_int(top), c_int(H),
                                      c_int(dtype_code(dt)), _stream()))

@@ -54,7 +54,8 @@ class GQAAttention(Mixer):
     A run item with `writes=False` projects q only and reads the cache another item wrote.
 
     Variations (`AttentionSpec`): biases on the projections, values of another width than keys, a bound on the scores
-    (softcap), a sink in the softmax's denominator and an output gate.  The gate's matrix is packed behind q, k and v,
+    (softcap), a sink in the softmax's denominator, an output gate, rotation of pairs (2i, 2i + 1), heads of q and k divided
+    by their root mean square after the rotation, and a mask in blocks of positions (its pages are a window group's).  The gate's matrix is packed behind q, k and v,
     the biases of q, k and v are added by the preparation kernel before the per-head norms, and bound, sink and gate
     are applied inside the attention kernels that take the steps of a layer that has any of them: in bfloat16 portions of
     prompts run on the tensor cores with float32 softmax weights (csrc/attention_mma.cu), single decoded tokens (their
@@ -95,7 +96,8 @@ class GQAAttention(Mixer):
     def varied(spec: AttentionSpec) -> bool:
         """True for a layer that only the general kernels take (see the class's last paragraph)."""
         return bool(spec.q_bias or spec.k_bias or spec.v_bias or spec.o_bias or spec.gate_proj or spec.sink or spec.softcap > 0
-                    or spec.value_dim != spec.head_dim)
+                    or spec.value_dim != spec.head_dim or spec.chunk or spec.unit_norm_eps is not None
+                    or (spec.position is not None and getattr(spec.position, "pairing", "half") != "half"))
 
     def __init__(self, spec: AttentionSpec, weights, dtype, device):
         if spec.num_heads % spec.num_kv_heads != 0:
@@ -139,6 +141,14 @@ class GQAAttention(Mixer):
         # kernels are told and refuse what they do not implement
         self.pairing = getattr(self.position, "pairing", "half") if self.position is not None else "half"
         self.head_norm = (spec.q_norm or spec.k_norm).kind if (spec.q_norm or spec.k_norm) else "rmsnorm"
+        if spec.unit_norm_eps is not None:
+            # no gains, and after the rotation (the preparation kernel's general form)
+            if spec.q_norm or spec.k_norm:
+                raise ValueError("attention: per-head norms before the rotation and a unit norm after it exclude each other")
+            self.head_norm, self.norm_eps = "unit_rms_after", float(spec.unit_norm_eps)
+        self.chunk = int(spec.chunk or 0)
+        if self.chunk and spec.window:
+            raise ValueError("attention: a window and a mask in blocks exclude each other")
         self.sm_count = ops.sm_count(device)
         self.window = int(spec.window or 0)
         self.bq = ops.attention_tile_queries(self.nq, self.nkv)
@@ -148,14 +158,17 @@ class GQAAttention(Mixer):
 
     # -- what the engine asks
     def cache_request(self) -> KVRequest:
-        return KVRequest(WINDOW if self.window else FULL, self.window, self.nkv, self.hd,
+        # a mask in blocks of `chunk` positions never looks further back than chunk - 1 keys: its pages are a
+        # window group's, given back as the blocks pass
+        held = self.window or self.chunk
+        return KVRequest(WINDOW if held else FULL, held, self.nkv, self.hd,
                          v_head_dim=self.vd if self.vd != self.hd else 0)
 
     def max_positions(self):
         return self.position.max_positions if self.position is not None else None
 
     def _tiles(self, builder, bq: int, heaviest_first: bool = False) -> None:
-        add_query_tiles(builder, bq, self.window, heaviest_first)
+        add_query_tiles(builder, bq, self.window or self.chunk, heaviest_first)
 
     def tc_tile_queries(self, page_size: int) -> int:
         if self.dtype != torch.bfloat16 or self.is_varied:
@@ -175,7 +188,7 @@ class GQAAttention(Mixer):
 
     def step_arrays_key(self):
         """Mixers with equal keys add the same arrays in `prepare_step`: the engine asks one of them."""
-        return ("attention_tiles", self.bq, self.nq, self.nkv, self.hd, self.window, str(self.dtype), self.is_varied)
+        return ("attention_tiles", self.bq, self.nq, self.nkv, self.hd, self.window, self.chunk, str(self.dtype), self.is_varied)
 
     def prepare_step(self, builder) -> None:
         """Tiles of queries, (sequence, first query of the tile) pairs, for the kernel this step will
@@ -196,8 +209,8 @@ class GQAAttention(Mixer):
         chunks = (G + 15) // 16
         blocks = max(1, ctx.n_seqs * self.nkv * chunks)
         longest = ctx.max_ctx_bound if ctx.fixed_shapes else ctx.max_ctx
-        if self.window:
-            longest = min(longest, self.window)
+        if self.window or self.chunk:
+            longest = min(longest, self.window or self.chunk)
         by_sms = (2 * self.sm_count + blocks - 1) // blocks
         by_len = max(1, longest // 128)
         parts = max(1, min(by_sms, by_len, 64))
@@ -292,7 +305,8 @@ class GQAAttention(Mixer):
             tile_seq = ctx.array(f"attention_tiles_bq{mma_bq}_seq")
             ops.attention_mma(o, q, cache.k, cache.v, group.block_tables, group.max_blocks, ctx.ctx_len, ctx.cu_q, tile_seq,
                               ctx.array(f"attention_tiles_bq{mma_bq}_q0"), tile_seq.numel(), self.nq, self.nkv, self.hd, self.vd,
-                              cache.page_size, self.window, float(self.spec.scale), softcap=self.softcap, sink=self.sink, gate=gate)
+                              cache.page_size, self.window, float(self.spec.scale), softcap=self.softcap, sink=self.sink, gate=gate,
+                              chunk=self.chunk)
             out = linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
             if self.o_bias is not None:
                 ops.add_bias(out, self.o_bias)
@@ -307,7 +321,7 @@ class GQAAttention(Mixer):
         ops.paged_attention(o, q, q.stride(0), cache.k, cache.v, group.block_tables, group.max_blocks,
                             ctx.ctx_len, ctx.cu_q, tile_seq, tile_q0, tile_seq.numel(), T, self.nq, self.nkv,
                             self.hd, cache.page_size, self.window, float(self.spec.scale), parts, part_size, scratch,
-                            vd=self.vd, softcap=self.softcap, sink=self.sink, gate=gate)
+                            vd=self.vd, softcap=self.softcap, sink=self.sink, gate=gate, chunk=self.chunk)
         out = linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
         if self.o_bias is not None:
             ops.add_bias(out, self.o_bias)

@@ -7,7 +7,8 @@ from .base import LayerCache, Part
 from .registry import (build_feed_forward, build_mixer, build_norm, feed_forward_class, mixer_class, norm_class,
                        register_block)
 from ..kernels import ops
-from .spec import PostNormBlockSpec, PreNormBlockSpec
+from .parallel import finish_pair
+from .spec import PostNormBlockSpec, PreNormBlockSpec, SandwichBlockSpec
 
 
 class PreNormBlock(Part):
@@ -54,7 +55,7 @@ class PreNormBlock(Part):
     def forward(self, ctx, resid: torch.Tensor, delta, cache: LayerCache):
         T, H = resid.shape
         x = self.mixer_norm.add_norm(resid, delta, ctx.workspace.buffer("block_normed", T, H, self.dtype))
-        mixed = self.mixer.forward(ctx, x, cache)
+        mixed = finish_pair(ctx, self.mixer.forward(ctx, x, cache), self.dtype)
         if self.ffn is None:
             return mixed          # a layer without a feed-forward: the next norm adds the mixer's output
         x = self.ffn_norm.add_norm(resid, mixed, ctx.workspace.buffer("block_normed", T, H, self.dtype))
@@ -127,5 +128,75 @@ class PostNormBlock(Part):
         return None
 
 
+class SandwichBlock(Part):
+    """x1 = x + norm_b(mixer(norm_a(x))); x2 = x1 + norm_d(ffn(norm_c(x1))): every sublayer reads a normed stream and has
+    its output normed before it joins the stream.
+
+    The residual stream is the one float32 buffer of every other block.  One kernel a sublayer does what lies between
+    two sublayers: `norm_add` normalises the sublayer's output (an array, float32 slices, or the weighted pair a parallel
+    mixer returns), adds it to the residual and writes the NEXT sublayer's normed input in the same pass (the next
+    block's first norm included, when the run list's next item is a block of this kind too: the model names it in
+    `ctx.next_block`).  A block whose input nobody prepared norms it with `add_rmsnorm`, which also finishes a sum the
+    block before left open."""
+
+    @staticmethod
+    def weight_decls(spec: SandwichBlockSpec):
+        decls = (norm_class(spec.mixer_norm).weight_decls(spec.mixer_norm) + mixer_class(spec.mixer).weight_decls(spec.mixer)
+                 + norm_class(spec.mixer_out_norm).weight_decls(spec.mixer_out_norm))
+        if spec.ffn is not None:
+            decls += (norm_class(spec.ffn_norm).weight_decls(spec.ffn_norm) + feed_forward_class(spec.ffn).weight_decls(spec.ffn)
+                      + norm_class(spec.ffn_out_norm).weight_decls(spec.ffn_out_norm))
+        return decls
+
+    @staticmethod
+    def kernel_modules(spec: SandwichBlockSpec):
+        mods = ("rowwise", "elementwise") + tuple(mixer_class(spec.mixer).kernel_modules(spec.mixer))
+        if spec.ffn is not None:
+            mods += tuple(feed_forward_class(spec.ffn).kernel_modules(spec.ffn))
+        return mods
+
+    def __init__(self, spec: SandwichBlockSpec, weights, dtype, device):
+        norms = [spec.mixer_norm, spec.mixer_out_norm] + ([spec.ffn_norm, spec.ffn_out_norm] if spec.ffn is not None else [])
+        for norm in norms:
+            if norm is None or norm.kind != "rmsnorm" or norm.weight_offset != 0.0:
+                raise ValueError("sandwich block: its norms are plain RMSNorms")
+        self.spec, self.dtype = spec, dtype
+        self.mixer_norm = build_norm(spec.mixer_norm, weights, dtype, device)
+        self.mixer = build_mixer(spec.mixer, weights, dtype, device)
+        self.mixer_out_norm = build_norm(spec.mixer_out_norm, weights, dtype, device)
+        self.ffn_norm = build_norm(spec.ffn_norm, weights, dtype, device) if spec.ffn is not None else None
+        self.ffn = build_feed_forward(spec.ffn, weights, dtype, device) if spec.ffn is not None else None
+        self.ffn_out_norm = build_norm(spec.ffn_out_norm, weights, dtype, device) if spec.ffn is not None else None
+
+    def workspace_bytes(self, tokens: int) -> int:
+        elem = 2 if self.dtype == torch.bfloat16 else 4
+        own = tokens * self.spec.mixer_norm.dim * elem
+        parts = [getattr(p, "workspace_bytes", None) for p in (self.mixer, self.ffn) if p is not None]
+        return own + max([f(tokens) for f in parts if f is not None] or [0])
+
+    def forward(self, ctx, resid: torch.Tensor, delta, cache: LayerCache):
+        T, H = resid.shape
+        normed = ctx.workspace.buffer("block_normed", T, H, self.dtype)
+        if delta is not None or getattr(ctx, "normed_for", None) is not self:
+            # nobody prepared this block's input: norm it here (and finish the sum a block of another kind left open)
+            self.mixer_norm.add_norm(resid, finish_pair(ctx, delta, self.dtype) if delta is not None else None, normed)
+        ctx.normed_for = None
+        # the block that runs next, if it is of this kind, finds its normed input ready
+        follower = getattr(ctx, "next_block", None)
+        follow = follower.mixer_norm if isinstance(follower, SandwichBlock) else None
+        mixed = self.mixer.forward(ctx, normed, cache)
+        nxt = self.ffn_norm if self.ffn is not None else follow
+        ops.norm_add(resid, mixed, self.mixer_out_norm.weight, self.mixer_out_norm.eps, normed if nxt is not None else None, self.dtype,
+                     next_gain=nxt.weight if nxt is not None else None, next_eps=nxt.eps if nxt is not None else 0.0)
+        if self.ffn is not None:
+            out = self.ffn.forward(ctx, normed)
+            nxt = follow
+            ops.norm_add(resid, out, self.ffn_out_norm.weight, self.ffn_out_norm.eps, normed if nxt is not None else None, self.dtype,
+                         next_gain=nxt.weight if nxt is not None else None, next_eps=nxt.eps if nxt is not None else 0.0)
+        ctx.normed_for = follower if follow is not None else None
+        return None
+
+
 register_block("prenorm", PreNormBlock)
+register_block("sandwich", SandwichBlock)
 register_block("postnorm", PostNormBlock)

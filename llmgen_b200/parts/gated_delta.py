@@ -92,7 +92,7 @@ class GatedDelta(Mixer):
                        ctx.state_slots, ctx.n_seqs, H, G, D, E, float(self.spec.unit_eps), float(D) ** -0.5,
                        beta_buf=ws.buffer("delta_beta", T, H + G, torch.float32))
         y = ws.buffer("delta_y", T, H * E, self.dtype)
-        ops.gated_rmsnorm(y.view(T * H, E), o.view(T * H, E), gate.view(T * H, E), self.norm_gain, self.norm_eps)
+        ops.gated_rmsnorm(y.view(T * H, E), o.view(T * H, E), gate, self.norm_gain, self.norm_eps, heads=H)
         return linear_sliced(ws, "mixer_out", y, self.w_o, self.dtype)
 
 

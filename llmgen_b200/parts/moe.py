@@ -7,7 +7,7 @@ from ..kernels import ops
 from .base import FeedForward
 from .linear import GEMM_MODULES, linear, linear_sliced
 from .registry import register_feed_forward
-from .spec import ClampedExpertSpec, DenseMLPSpec, RoutedMLPSpec, WeightDecl
+from .spec import VECTOR, ClampedExpertSpec, DenseMLPSpec, GatedExpertSpec, RoutedMLPSpec, WeightDecl
 
 
 class DenseMLP(FeedForward):
@@ -43,7 +43,16 @@ class DenseMLP(FeedForward):
         return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype)
 
 
-def _expert_decls(e: ClampedExpertSpec, hidden: int):
+def _expert_form(e):
+    """(activation of `act_rows`, alpha, limit, plain gated unit?) of an expert's spec."""
+    if isinstance(e, GatedExpertSpec):
+        if e.activation != "silu":
+            raise ValueError(f"routed feed-forward: expert activation {e.activation!r} is not supported")
+        return "silu_glu", 1.0, 0.0, True
+    return "clamped_glu", float(e.alpha), float(e.limit), False
+
+
+def _expert_decls(e, hidden: int):
     return [WeightDecl(e.gate_proj, (e.intermediate_size, hidden)), WeightDecl(e.up_proj, (e.intermediate_size, hidden)),
             WeightDecl(e.down_proj, (hidden, e.intermediate_size))]
 
@@ -58,7 +67,7 @@ class RoutedMLP(FeedForward):
     plan and sum:
 
       bfloat16   tiles of 128 rows, every expert's rows starting on a tile: `moe_gather` copies the rows (times their
-                 weights) into that order, and the grouped tensor-core product (`gemm_tc_grouped`: TMA, tcgen05.mma,
+                 weights, where the weight is on the expert's input; else `moe_combine` applies it) into that order, and the grouped tensor-core product (`gemm_tc_grouped`: TMA, tcgen05.mma,
                  the expert of each tile read from the device) runs gate/up of all experts in one launch, the clamped
                  gated activation follows row-wise, and a second grouped launch runs down
       float32    (and operands TMA refuses) tiles of 16 rows through `moe_experts`, float32 sums on the CUDA cores
@@ -70,6 +79,8 @@ class RoutedMLP(FeedForward):
     @staticmethod
     def weight_decls(spec: RoutedMLPSpec):
         decls = [WeightDecl(spec.router, (len(spec.experts), spec.hidden_size))]
+        if spec.router_bias:
+            decls.append(WeightDecl(spec.router_bias, (len(spec.experts),), VECTOR))
         for e in spec.experts:
             decls += _expert_decls(e, spec.hidden_size)
         if spec.shared is not None:
@@ -82,8 +93,9 @@ class RoutedMLP(FeedForward):
 
     def __init__(self, spec: RoutedMLPSpec, weights, dtype, device):
         first = spec.experts[0]
-        if any((e.intermediate_size, e.limit, e.alpha) != (first.intermediate_size, first.limit, first.alpha) for e in spec.experts):
-            raise ValueError("routed feed-forward: all routed experts share one size, limit and alpha")
+        if any((type(e), e.intermediate_size, _expert_form(e)) != (type(first), first.intermediate_size, _expert_form(first))
+               for e in spec.experts):
+            raise ValueError("routed feed-forward: all routed experts share one kind, size and constants")
         if not 0 < spec.top_k <= len(spec.experts):
             raise ValueError(f"routed feed-forward: top {spec.top_k} of {len(spec.experts)} experts")
         if spec.scoring not in ops.ROUTER_SCORINGS:
@@ -91,13 +103,16 @@ class RoutedMLP(FeedForward):
         self.spec, self.dtype = spec, dtype
         self.E, self.top, self.F = len(spec.experts), spec.top_k, first.intermediate_size
         self.router = weights.device_tensor(spec.router, torch.float32, device)      # routing is float32 in both dtypes
+        self.router_bias = weights.device_tensor(spec.router_bias, dtype, device).contiguous() if spec.router_bias else None
+        self.act, self.alpha, self.limit, self.plain = _expert_form(first)
+        self.shared_form = _expert_form(spec.shared) if spec.shared is not None else None
         stack = lambda names: torch.stack([weights.device_tensor(n, dtype, device, keep=False) for n in names]).contiguous()
         self.w_gate = stack([e.gate_proj for e in spec.experts])     # [E, F, H]
         self.w_up = stack([e.up_proj for e in spec.experts])         # [E, F, H]
         self.w_down = stack([e.down_proj for e in spec.experts])     # [E, H, F]
         # the tensor-core path reads gate and up as one matrix per expert, [E, 2F, H]: gate rows, then up rows
         H = spec.hidden_size
-        self.grouped = dtype == torch.bfloat16 and H % 8 == 0 and self.F % 8 == 0 and spec.weight_on_input
+        self.grouped = dtype == torch.bfloat16 and H % 8 == 0 and self.F % 8 == 0
         if self.grouped:
             self.w_gate_up = torch.cat([self.w_gate, self.w_up], dim=1).contiguous()
             self.w_gate = self.w_up = None
@@ -127,9 +142,8 @@ class RoutedMLP(FeedForward):
         slot_expert, pos_of_slot, order = ints[:n_slots], ints[n_slots:2 * n_slots], ints[2 * n_slots:2 * n_slots + n_rows]
         tile_expert, tile_start, tile_rows = (ints[2 * n_slots + n_rows + i * tiles:2 * n_slots + n_rows + (i + 1) * tiles] for i in range(3))
         slot_weight = ws.flat("moe_weights", n_slots, torch.float32)
-        ops.moe_route(x, self.router, slot_expert, slot_weight, top, spec.scoring, spec.renormalize)
+        ops.moe_route(x, self.router, slot_expert, slot_weight, top, spec.scoring, spec.renormalize, bias=self.router_bias)
         ops.moe_plan(slot_expert, n_slots, self.E, order, pos_of_slot, tile_expert, tile_start, tile_rows, tile=tile, padded=self.grouped)
-        first = spec.experts[0]
         cap = (ws.default_rows * top // 128 + self.E) * 128 if self.grouped else ws.default_rows * top
         rows = ws.buffer("moe_rows", n_rows, H, torch.float32, capacity_rows=cap)
         if self.grouped:
@@ -138,12 +152,12 @@ class RoutedMLP(FeedForward):
             gate_up = ws.buffer("moe_gate_up", n_rows, 2 * self.F, self.dtype, capacity_rows=cap)
             ops.gemm_tc_grouped(gate_up, xs, self.w_gate_up, tile_expert, real_rows=n_slots)
             y = ws.buffer("moe_act", n_rows, self.F, self.dtype, capacity_rows=cap)
-            ops.act_rows(y, gate_up, "clamped_glu", alpha=first.alpha, limit=first.limit)
+            ops.act_rows(y, gate_up, self.act, alpha=self.alpha, limit=self.limit)
             ops.gemm_tc_grouped(rows, y, self.w_down, tile_expert, real_rows=n_slots)
         else:
             y = ws.buffer("moe_act", n_rows, self.F, torch.float32, capacity_rows=cap)
             ops.moe_experts(y, x, self.w_gate, self.w_up, order, slot_weight, tile_expert, tile_start, tile_rows, n_slots, top,
-                            first=True, weight_on_input=spec.weight_on_input, alpha=first.alpha, limit=first.limit)
+                            first=True, weight_on_input=spec.weight_on_input, alpha=self.alpha, limit=self.limit, plain=self.plain)
             ops.moe_experts(rows, y, self.w_down, None, order, slot_weight, tile_expert, tile_start, tile_rows, n_slots, top,
                             first=False, weight_on_input=spec.weight_on_input)
         shared_out = None
@@ -151,10 +165,12 @@ class RoutedMLP(FeedForward):
             Fs = spec.shared.intermediate_size
             gate_up = linear_sliced(ws, "moe_shared_gate_up", x, self.shared_gate_up, self.dtype)
             act = ws.buffer("moe_shared_act", T, Fs, self.dtype)
-            ops.act_rows(act, gate_up, "clamped_glu", alpha=spec.shared.alpha, limit=spec.shared.limit)
+            ops.act_rows(act, gate_up, self.shared_form[0], alpha=self.shared_form[1], limit=self.shared_form[2])
             shared_out = linear(act, self.shared_down, ws.buffer("moe_shared_out", T, H, self.dtype))
         out = ws.flat("moe_out", T * H, torch.float32).view(1, T, H)
-        ops.moe_combine(out[0], rows, pos_of_slot, shared_out, top)
+        # the grouped products leave an expert's plain output: a weight on the output is applied as the rows are added
+        ops.moe_combine(out[0], rows, pos_of_slot, shared_out, top,
+                        slot_weight=slot_weight if self.grouped and not spec.weight_on_input else None)
         return ops.Partials(out)
 
 

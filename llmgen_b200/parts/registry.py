@@ -105,6 +105,8 @@ def model_weight_decls(model_spec) -> List[WeightDecl]:
     """Every tensor a whole model reads, in declaration order."""
     _ensure_builtin()
     decls = [WeightDecl(model_spec.embedding, (model_spec.vocab_size, model_spec.hidden_size))]
+    if getattr(model_spec, "embedding_norm", None) is not None:
+        decls += norm_class(model_spec.embedding_norm).weight_decls(model_spec.embedding_norm)
     for layer in model_spec.layers:
         decls += block_class(layer).weight_decls(layer)
     from .reentry import Reentry
@@ -139,5 +141,5 @@ def _ensure_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from . import (attention, block, gated_delta, latent_attention, linear_attention, mlp, moe, norm,  # noqa: F401
-                       rglru, rope)
+        from . import (attention, block, decay_attention, gated_delta, latent_attention, linear_attention, mlp,  # noqa: F401
+                       moe, norm, parallel, rglru, rope)

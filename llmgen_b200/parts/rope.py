@@ -1,6 +1,7 @@
 """Rotary position encoding: the cos/sin tables its mixer's kernel reads."""
 from __future__ import annotations
 
+import math
 from typing import Dict, Tuple
 
 import torch
@@ -12,20 +13,36 @@ from .spec import RopeSpec
 _TABLES: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
 
 
+def scale_by_wavelength(inv: torch.Tensor, factor: float, low: float, high: float, original: float) -> torch.Tensor:
+    """Frequencies (float64) scaled by their wavelength l = 2 pi / f: unchanged where l < original / high, divided by
+    `factor` where l > original / low, and between the two (1 - s) f / factor + s f with
+    s = (original / l - low) / (high - low)."""
+    if high <= low:
+        raise ValueError(f"rotary scaling: high {high} must exceed low {low}")
+    wave = 2.0 * math.pi / inv
+    s = (original / wave - low) / (high - low)
+    blended = (1.0 - s) * inv / factor + s * inv
+    return torch.where(wave < original / high, inv, torch.where(wave > original / low, inv / factor, blended))
+
+
 class Rope(Part):
     """cos/sin of pos / theta^(2i / rotary_dim), i in [0, rotary_dim/2), for every position:
     computed once on the host in float64 and kept as float32 [max_positions, rotary_dim/2]
     (the reference computes inverse frequencies and angles in f64 and stores f32 rows whose two
     halves are equal, src/backend/cpu/rope.zig:47-75; only one half is kept here).  Layers
-    with the same spec share one pair of tables."""
+    with the same spec share one pair of tables.  `spec.scaling` rescales the frequencies by their wavelength first
+    (`scale_by_wavelength`)."""
 
     def __init__(self, spec: RopeSpec, weights, dtype, device):
         self.spec = spec
-        key = (spec.rotary_dim, float(spec.theta), spec.max_positions, str(device))
+        scaling = tuple(float(v) for v in spec.scaling) if getattr(spec, "scaling", None) is not None else None
+        key = (spec.rotary_dim, float(spec.theta), spec.max_positions, scaling, str(device))
         if key not in _TABLES:
             half = spec.rotary_dim // 2
             inv = 1.0 / torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64),
                                   torch.arange(0, half, dtype=torch.float64) * 2.0 / spec.rotary_dim)
+            if scaling is not None:
+                inv = scale_by_wavelength(inv, *scaling)
             ang = torch.arange(spec.max_positions, dtype=torch.float64)[:, None] * inv[None, :]
             _TABLES[key] = (ang.cos().to(torch.float32).to(device).contiguous(),
                             ang.sin().to(torch.float32).to(device).contiguous())

@@ -62,6 +62,10 @@ class RopeSpec:
     theta: float
     max_positions: int
     pairing: str = "half"
+    # Frequencies scaled by wavelength, (factor, low, high, original): with f_i = theta^(-2i/rotary_dim) and wavelength
+    # l = 2 pi / f, f stays where l < original / high, becomes f / factor where l > original / low, and between the two
+    # (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  None: the plain frequencies.
+    scaling: Optional[Tuple[float, float, float, float]] = None
     kind: str = "rope"
 
 
@@ -103,6 +107,12 @@ class AttentionSpec:
     softcap: float = 0.0
     sink: bool = False
     gate_proj: Optional[str] = None
+    # `unit_norm_eps`: after the rotation, every head of q and k is divided by its root mean square,
+    # x / sqrt(mean(x^2) + unit_norm_eps), without gains (in place of `q_norm` / `k_norm`, which come before the rotation).
+    # `chunk`: a query sees the keys at or before it that lie in its own block of `chunk` positions,
+    # floor(j / chunk) = floor(i / chunk), blocks counted from the sequence's first position.
+    unit_norm_eps: Optional[float] = None
+    chunk: Optional[int] = None
     kind: str = "attention"
 
     @property
@@ -242,6 +252,72 @@ class GatedDeltaSpec:
     kind: str = "gated_delta"
 
 
+@dataclass(frozen=True)
+class ChannelDecayAttentionSpec:
+    """Linear attention whose state forgets by a decay per head and key channel that the token itself decides.
+
+    q = x Wq^T * key_dim^(-1/2), k = x Wk^T [heads, key_dim], v = x Wv^T [heads, value_dim]; the decay
+    a = sigmoid(z)^(1 / tau), z = (x Wa1^T) Wa2^T + bias, [heads, key_dim].  Per head, S [key_dim, value_dim] float32, zero
+    before the first token:  S_t = diag(a_t) S_(t-1) + k_t v_t^T,  o_t = S_t^T q_t.  Each head's o passes an RMSNorm over
+    value_dim (`out_norm`, one gain vector for all heads), the heads side by side are multiplied by silu(x Wg^T) and projected
+    by Wo.  State per request: S."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    tau: float
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    gate_proj: str
+    o_proj: str
+    decay_down: str                      # Wa1 [rank, hidden]
+    decay_up: str                        # Wa2 [heads key_dim, rank]
+    decay_bias: str                      # [heads key_dim]
+    out_norm: RMSNormSpec
+    decay_rank: int = 16
+    kind: str = "channel_decay_attention"
+
+
+@dataclass(frozen=True)
+class TokenShiftDecaySpec:
+    """Time mixing over blends of each token with the one before it, with a decay per head and key channel and a bonus
+    for the token's own key.
+
+    With x' the row of the token before (zeros before the first), each of r, k, v, g, w reads its own blend
+    m_s = x + (x' - x) mu_s.  r, k, v = W m [heads, head_dim]; gate = silu(Wg m_g); the decay
+    w = exp(-exp(Ww2 tanh(Ww1 m_w) + w0)) [heads, head_dim].  Per head, S [head_dim, head_dim] float32, zero before the
+    first token:  o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t,  S_t = diag(w_t) S_(t-1) + k_t v_t^T.  Each head's o is divided by
+    its root mean square (eps inside the root); the heads side by side are multiplied by `out_gain`, by the gate, and
+    projected by Wo.  State per request: S and the last row of x."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    eps: float
+    mix: Tuple[str, str, str, str, str]  # mu of r, k, v, g, w: [hidden] each
+    r_proj: str
+    k_proj: str
+    v_proj: str
+    gate_proj: str
+    o_proj: str
+    decay_down: str                      # Ww1 [rank, hidden]
+    decay_up: str                        # Ww2 [heads head_dim, rank]
+    decay_bias: str                      # w0 [heads head_dim]
+    bonus: str                           # u [heads, head_dim]
+    out_gain: str                        # [heads head_dim]
+    decay_rank: int = 16
+    kind: str = "token_shift_decay"
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Several mixers side by side that read the same input: the result is sum_i scales[i] * branches[i](x).  At most
+    one branch keeps paged keys and values; the states of the branches that keep one lie side by side in one row."""
+    branches: Tuple[object, ...]
+    scales: Tuple[float, ...]
+    kind: str = "parallel"
+
+
 # ---------------------------------------------------------------------- feed-forwards
 @dataclass(frozen=True)
 class DenseMLPSpec:
@@ -267,18 +343,31 @@ class ClampedExpertSpec:
 
 
 @dataclass(frozen=True)
+class GatedExpertSpec:
+    """One small gated feed-forward: (act(x Wgate^T) * (x Wup^T)) Wdown^T, act = silu; no biases."""
+    intermediate_size: int
+    gate_proj: str
+    up_proj: str
+    down_proj: str
+    activation: str = "silu"
+
+
+@dataclass(frozen=True)
 class RoutedMLPSpec:
-    """Mixture of experts: router scores s = sigmoid(x Wr^T) (or softmax) in float32, the `top_k` largest choose
-    experts, their scores are the weights (renormalised over the chosen ones if `renormalize`).  The weight multiplies
-    the expert's input (`weight_on_input`) or its output.  An optional shared expert runs for every token and is added."""
+    """Mixture of experts: router scores s = sigmoid(x Wr^T + b) (or softmax) in float32, the `top_k` largest choose
+    experts, their scores are the weights (renormalised over the chosen ones if `renormalize`); with scoring
+    "softmax_top" the logits themselves choose and the weights are the softmax over the chosen logits alone.  The weight
+    multiplies the expert's input (`weight_on_input`) or its output.  An optional shared expert runs for every token and
+    is added.  Experts are `ClampedExpertSpec` or `GatedExpertSpec`, all routed ones of one kind and size."""
     hidden_size: int
     router: str
-    experts: Tuple[ClampedExpertSpec, ...]
+    experts: Tuple[object, ...]
     top_k: int
-    shared: Optional[ClampedExpertSpec] = None
+    shared: Optional[object] = None
     scoring: str = "sigmoid"
     renormalize: bool = False
     weight_on_input: bool = True
+    router_bias: Optional[str] = None
     kind: str = "routed_mlp"
 
 
@@ -325,6 +414,19 @@ class PostNormBlockSpec:
 
 
 @dataclass(frozen=True)
+class SandwichBlockSpec:
+    """x1 = x + norm_b(mixer(norm_a(x))); x2 = x1 + norm_d(ffn(norm_c(x1))): a norm on each sublayer's input and another on
+    its output.  `ffn` (with its two norms) may be None: a layer without a feed-forward."""
+    mixer_norm: object
+    mixer: object
+    mixer_out_norm: object
+    ffn_norm: Optional[object] = None
+    ffn: Optional[object] = None
+    ffn_out_norm: Optional[object] = None
+    kind: str = "sandwich"
+
+
+@dataclass(frozen=True)
 class ReentrySpec:
     """What happens to the residual stream before a run item: x <- [x | x0] W^T + table[row], with x0 the embedding's
     output of the same token, W [hidden, 2 hidden] (the stream's columns first) and `table` [rows, hidden]."""
@@ -368,6 +470,7 @@ class ModelSpec:
     embedding_scale: float = 1.0         # rows of the table are multiplied by this as they enter the residual
     logit_cap: float = 0.0               # > 0: logits = cap * tanh(logits / cap)
     logit_scale: float = 1.0             # logits are multiplied by this (before the cap)
+    embedding_norm: Optional[object] = None   # a norm spec: the embedding's rows pass it before they become the residual
     # Tensors that a model folder of this architecture may carry although the model reads none of them
     # (shell patterns), and (name, declared name) pairs of such tensors that must then hold the same values.
     ignorable_tensors: Tuple[str, ...] = ()
