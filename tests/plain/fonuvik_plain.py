@@ -104,6 +104,26 @@ def chunked_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps:
     return out.reshape(T, H * E) @ w["o"].T
 
 
+def decay_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, state: Optional[torch.Tensor] = None,
+                     bonus: Optional[torch.Tensor] = None):
+    """q, k, a [T, heads, dim], v [T, heads, vdim]; S [heads, dim, vdim] starts at `state` or zero.
+    Without `bonus`: S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t.
+    With `bonus` u [heads, dim]: o_t = (S_(t-1) + diag(u) k_t v_t^T)^T q_t, then the same update.
+    Returns (o [T, heads, vdim], the last S)."""
+    T, H, D = q.shape
+    E = v.shape[2]
+    S = torch.zeros(H, D, E, dtype=q.dtype) if state is None else state.clone()
+    o = torch.zeros(T, H, E, dtype=q.dtype)
+    for t in range(T):
+        kv = k[t][:, :, None] * v[t][:, None, :]
+        if bonus is not None:
+            o[t] = torch.einsum("hde,hd->he", S + bonus[:, :, None] * kv, q[t])
+        S = a[t][:, :, None] * S + kv
+        if bonus is None:
+            o[t] = torch.einsum("hde,hd->he", S, q[t])
+    return o, S
+
+
 def channel_decay_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: float,
                             state: Optional[torch.Tensor] = None):
     """Returns (output [T, width], final state [heads, dim, vdim])."""
@@ -114,11 +134,7 @@ def channel_decay_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict
     v = (h @ w["v"].T).view(T, H, E)
     z = (h @ w["a1"].T) @ w["a2"].T + w["a2.b"]
     a = torch.exp(torch.nn.functional.logsigmoid(z) / float(m["tau"])).view(T, H, D)
-    S = torch.zeros(H, D, E, dtype=h.dtype) if state is None else state.clone()
-    o = torch.zeros(T, H, E, dtype=h.dtype)
-    for t in range(T):
-        S = a[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hde,hd->he", S, q[t])
+    o, S = decay_recurrence(q, k, v, a, state)
     o = rms_norm(o, w["norm"], eps).reshape(T, H * E)
     return (o * silu(h @ w["g"].T)) @ w["o"].T, S
 
@@ -143,12 +159,7 @@ def token_shift_decay(h: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps:
     gate = silu(mix["g"] @ w["g"].T)
     decay = torch.exp(-torch.exp(torch.tanh(mix["w"] @ w["w1"].T) @ w["w2"].T + w["w0"])).view(T, H, D)
     u = w["u"].view(H, D)
-    S = torch.zeros(H, D, D, dtype=h.dtype) if state is None else state.clone()
-    o = torch.zeros(T, H, D, dtype=h.dtype)
-    for t in range(T):
-        kv = k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hde,hd->he", S + u[:, :, None] * kv, r[t])
-        S = decay[t][:, :, None] * S + kv
+    o, S = decay_recurrence(r, k, v, decay, state, bonus=u)
     o = rms_norm(o, None, eps).reshape(T, H * D) * w["norm"]
     return (o * gate) @ w["o"].T, h[-1].clone(), S
 
