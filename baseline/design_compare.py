@@ -1,9 +1,11 @@
-"""`bench.py --designs`: Derupel (or, with `--designs-family sarulix`, Sarulix) beside Qwen3 at equal layer sizes, random
-weights, one B200.
+"""`bench.py --designs`: Derupel (or, with `--designs-family sarulix` or `fonuvik`, that design) beside Qwen3 at equal
+layer sizes, random weights, one B200.
 
 For each size two models are built: a Derupel whose layers alternate its two mixers and its two feed-forwards (a Sarulix
 whose four layers are a recurrent unit, the delta rule, attention and a recurrent unit again, each with a feed-forward,
-entered once through its loop's mixing step), and the Qwen3 of the same width, depth, feed-forward width and vocabulary.
+entered once through its loop's mixing step; a Fonuvik whose layers alternate the parallel mixer and the token-shift
+mixer, each with a routed feed-forward whose chosen and shared experts together are as wide as the dense one), and the
+Qwen3 of the same width, depth, feed-forward width and vocabulary.
 Measured for both:
 
   prefill   one prompt of 2,048 tokens through one step (the graph of its shape replayed), tokens/s and ms
@@ -59,7 +61,20 @@ def sarulix_config(s: dict) -> dict:
             "logit_scale": 1.0, "loop": {"start": 0, "stop": len(layers), "times": 1}, "layers": layers, "max_positions": CONTEXT}
 
 
-FAMILIES = {"derupel": derupel_config, "sarulix": sarulix_config}
+def fonuvik_config(s: dict) -> dict:
+    W, heads, hd = s["width"], s["heads"], s["hd"]
+    routed = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"]}, "expert": {"ff": s["expert_ff"]},
+              "shared": {"ff": s["ff"] - s["top"] * s["expert_ff"]}}
+    left = {"heads": heads, "kv_heads": max(1, heads // 2), "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": 1024},
+            "rot": {"base": 500000.0, "dims": hd // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    right = {"heads": max(1, heads // 2), "dim": hd, "vdim": hd, "tau": 16.0, "decay_rank": 64}
+    par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 0.5}, "mlp": routed}
+    shift = {"type": "wkv", "mixer": {"heads": W // 64, "dim": 64, "decay_rank": 64}, "mlp": routed}
+    layers = [par if i % 2 == 0 else shift for i in range(s["layers"])]
+    return {"architecture": "Fonuvik", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6}, "layers": layers, "max_positions": CONTEXT}
+
+
+FAMILIES = {"derupel": derupel_config, "sarulix": sarulix_config, "fonuvik": fonuvik_config}
 
 
 def qwen3_config(s: dict) -> dict:

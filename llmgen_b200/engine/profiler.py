@@ -251,6 +251,8 @@ def _nbytes(x) -> int:
     """Bytes of an operand: an array, the slices of a product cut along K, or nothing."""
     if x is None:
         return 0
+    if hasattr(x, "first") and hasattr(x, "second"):       # ops.WeightedPair
+        return _nbytes(x.first) + _nbytes(x.second)
     tensor = getattr(x, "tensor", None)                    # ops.Partials
     if tensor is not None:
         return tensor.numel() * tensor.element_size()
@@ -277,6 +279,13 @@ class PassInfo:
             return sum(s + n for s, n in zip(self.starts, self.q_lens))
         return sum(min(s + n, window + n - 1) for s, n in zip(self.starts, self.q_lens))
 
+    def visible_keys_in_blocks(self, block: int) -> int:
+        """The same sum under a mask in blocks of `block` positions: position p sees the p % block + 1 keys of its block."""
+        return sum(p % block + 1 for s, n in zip(self.starts, self.q_lens) for p in range(s, s + n))
+
+    def keys_read_in_blocks(self, block: int) -> int:
+        return sum(s + n - s // block * block for s, n in zip(self.starts, self.q_lens))
+
 
 def _cost_product(a, info: PassInfo) -> Tuple[int, int]:
     w = a["w"]
@@ -291,8 +300,9 @@ def _cost_attention(a, info: PassInfo) -> Tuple[int, int]:
     elem = a["kcache"].element_size()
     tokens = sum(info.q_lens)
     vd = int(a.get("vd") or 0) or hd                       # values of their own width
-    flops = 2 * nq * (hd + vd) * info.visible_keys(window)
-    bytes_ = nkv * (hd + vd) * elem * info.keys_read(window) + tokens * nq * (hd + vd) * elem
+    block = int(a.get("chunk") or 0)                       # a mask in blocks: only the own block's keys are seen and read
+    flops = 2 * nq * (hd + vd) * (info.visible_keys_in_blocks(block) if block else info.visible_keys(window))
+    bytes_ = nkv * (hd + vd) * elem * (info.keys_read_in_blocks(block) if block else info.keys_read(window)) + tokens * nq * (hd + vd) * elem
     packed = a.get("packed")
     if packed is not None:                                 # the kernel also reads the projection and stores k, v
         bytes_ += _nbytes(packed) + 2 * tokens * int(a.get("nk") or 0) * hd * elem
@@ -361,6 +371,24 @@ def _cost_delta_scan(a, info: PassInfo) -> Tuple[int, int]:
     return flops, bytes_
 
 
+def _cost_decay_scan(a, info: PassInfo) -> Tuple[int, int]:
+    H, D, E = int(a["heads"]), int(a["dim"]), int(a["vdim"])
+    n = a["out"].shape[0]
+    flops = n * H * (6 * D * E + 14 * D)                   # decay, read-out and update over the state, a token; the preparation
+    # the preparation reads q, k, v and the pre-activations and writes their float32 row and 1 - a; the scan reads both
+    bytes_ = sum(_nbytes(a[k]) for k in ("q", "k", "v")) + 3 * _nbytes(a["decay"]) + 2 * n * (2 * H * D + H * E) * 4 \
+        + _nbytes(a["out"]) + 2 * len(info.q_lens) * H * D * E * 4
+    return flops, bytes_
+
+
+def _cost_token_shift(a, info: PassInfo) -> Tuple[int, int]:
+    return 3 * a["out"].numel(), _nbytes(a["out"]) + 2 * _nbytes(a["x"]) + _nbytes(a["mu"])
+
+
+def _cost_scaled_sum(a, info: PassInfo) -> Tuple[int, int]:
+    return 3 * a["out"].numel(), _nbytes(a["out"]) + _nbytes(a["pair"])
+
+
 def _cost_latent_attention(a, info: PassInfo) -> Tuple[int, int]:
     heads, rank, rot = int(a["heads"]), int(a["rank"]), int(a["rot"])
     tokens = sum(info.q_lens)
@@ -427,6 +455,7 @@ OP_COSTS: Dict[str, Callable] = {
     "attention_tc": _cost_attention, "attention_mma": _cost_attention, "sample": _cost_all_operands,
     "short_conv": _cost_short_conv, "rglru": _cost_rglru, "delta_scan": _cost_delta_scan, "add_bias": _cost_all_operands,
     "concat_stream": _cost_all_operands, "logit_cap": _cost_all_operands,
+    "decay_scan": _cost_decay_scan, "token_shift_mix": _cost_token_shift, "scaled_sum": _cost_scaled_sum,
 }
 
 
