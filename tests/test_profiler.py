@@ -285,7 +285,9 @@ def test_every_listed_binding_exists_with_the_operands_its_cost_reads():
              pf._cost_latent_absorb: [("q",), ("qa",), ("wuk",), ("heads",), ("dim",), ("rank",)],
              pf._cost_latent_expand: [("out",), ("oa",), ("wuv",), ("heads",), ("rank",), ("vdim",)],
              pf._cost_latent_prep: [("packed",), ("q_rank",), ("rank",), ("rot",)], pf._cost_latent_rotate: [("qa",), ("heads",), ("rot",)], pf._cost_moe_route: [("h",), ("router",)],
-             pf._cost_moe_experts: [("w0",), ("n_slots",), ("first",)], pf._cost_grouped_product: [("w",), ("a",), ("out",), ("real_rows",)]}
+             pf._cost_moe_experts: [("w0",), ("n_slots",), ("first",)], pf._cost_grouped_product: [("w",), ("a",), ("out",), ("real_rows",)],
+             pf._cost_decay_scan: [("heads",), ("dim",), ("vdim",), ("q",), ("k",), ("v",), ("decay",), ("out",)],
+             pf._cost_token_shift: [("out",), ("x",), ("mu",)], pf._cost_scaled_sum: [("out",), ("pair",)]}
     for name, cost in pf.OP_COSTS.items():
         params = inspect.signature(getattr(ops, name)).parameters
         for alternatives in needs[cost]:
