@@ -20,6 +20,7 @@
 // Every state is float32; gates, decays, their logarithms and exponentials, unit norms and the recurrences are float32
 // arithmetic in both storage dtypes.  The arithmetic of a token does not depend on where a step was cut.
 #include "common.cuh"
+#include <algorithm>
 
 LLMK_DEFINE_LAST_ERROR()
 
@@ -891,12 +892,29 @@ __global__ void __launch_bounds__(256) decay_prep_kernel(float* __restrict__ qkv
     }
 }
 
-template <int DSL, int SL, bool READ_FIRST>
-__global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p) {
+// Long sequences are walked in segments side by side (PART 1, then PART 2); PART 0 walks whole sequences.  With
+// S_end = diag(P) S_start + L for a segment (P the product of its decays, L its state from nothing):
+//   PART 1   segment 0 of a sequence runs as in PART 0, from the request's state and with its read-outs, and leaves its
+//            end state; every later segment but the last starts from nothing, reads nothing out and leaves L and P
+//            (P = exp(sum log1p(-(1 - a))): a running product would round at every token, the same way where decays
+//            hardly change)
+//   PART 2   every segment but the first folds the states before it into its start (S <- P_i S + L_i, a few reads of the
+//            state a block), walks its tokens with their read-outs, and the last leaves the request's state
+// A token's arithmetic is PART 0's; what differs is the grouping of the sums that make a segment's start.
+struct DecaySegments {
+    float* state;            // [n_seqs * max_segs][H][D][E]: segment j of sequence s at s * max_segs + j
+    float* decay;            // [n_seqs * max_segs][H][D]: P
+    int seg_len, max_segs;
+};
+
+template <int DSL, int SL, bool READ_FIRST, int PART>
+__global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p, DecaySegments g) {
     using Sh = DeltaShape<DSL, SL>;
     constexpr int ROW = Sh::ROW, COLS = Sh::COLS, STRIDE = Sh::STRIDE, BUF = Sh::BUF;
     extern __shared__ __align__(16) float sm[];
-    const int s = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * COLS;
+    const int s = PART == 0 ? blockIdx.x : blockIdx.x / g.max_segs;
+    const int j = PART == 0 ? 0 : blockIdx.x % g.max_segs;
+    const int h = blockIdx.y, e0 = blockIdx.z * COLS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int slice = lane % SL, col = warp * (32 / SL) + lane / SL;
     const int e = e0 + col;
@@ -905,15 +923,50 @@ __global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p
     for (int i = threadIdx.x; i < 2 * BUF; i += DELTA_THREADS) sm[i] = 0.f;
     pdl_launch_dependents();
     pdl_wait();
-    const int q_beg = p.cu_q[s], n = p.cu_q[s + 1] - q_beg;
+    int q_beg = p.cu_q[s], n = p.cu_q[s + 1] - q_beg;
     if (n <= 0) return;
+    int n_segs = 1;
+    if (PART != 0) {
+        n_segs = ceil_div(n, g.seg_len);
+        if (j >= n_segs || (PART == 1 && j > 0 && j == n_segs - 1) || (PART == 2 && j == 0)) return;
+        q_beg += j * g.seg_len;
+        n = min(g.seg_len, n - j * g.seg_len);
+    }
+    const bool read_out = PART != 1 || j == 0;
     const int slot = p.state_slots[s];
     float S[DSL];
     float* st = slot >= 0 ? p.state + (size_t)slot * p.state_ld + (size_t)h * D * E : nullptr;
+    const size_t seg_first = (size_t)s * (PART == 0 ? 0 : g.max_segs);
+    if (PART == 2) {
+        const float* L = g.state + (seg_first * p.H + h) * (size_t)D * E;
 #pragma unroll
-    for (int i = 0; i < DSL; ++i) {
-        const int d = slice * DSL + i;
-        S[i] = (st && d < D && e < E) ? st[(size_t)d * E + e] : 0.f;
+        for (int i = 0; i < DSL; ++i) {
+            const int d = slice * DSL + i;
+            S[i] = (d < D && e < E) ? L[(size_t)d * E + e] : 0.f;
+        }
+        for (int seg = 1; seg < j; ++seg) {
+            const float* Ls = g.state + ((seg_first + seg) * p.H + h) * (size_t)D * E;
+            const float* Ps = g.decay + ((seg_first + seg) * p.H + h) * (size_t)D;
+#pragma unroll
+            for (int i = 0; i < DSL; ++i) {
+                const int d = slice * DSL + i;
+                if (d < D && e < E) S[i] = fmaf(Ps[d], S[i], Ls[(size_t)d * E + e]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < DSL; ++i) {
+            const int d = slice * DSL + i;
+            S[i] = (j == 0 && st && d < D && e < E) ? st[(size_t)d * E + e] : 0.f;
+        }
+    }
+    if (PART == 1 && j > 0 && blockIdx.z == 0) {
+        for (int d = threadIdx.x; d < D; d += DELTA_THREADS) {
+            const float* c = p.decay + (size_t)q_beg * ((size_t)p.H * D) + (size_t)h * D + d;
+            float sum = 0.f;
+            for (int t = 0; t < n; ++t) sum += log1pf(-c[(size_t)t * ((size_t)p.H * D)]);
+            g.decay[((seg_first + j) * p.H + h) * (size_t)D + d] = expf(sum);
+        }
     }
     __syncthreads();
     delta_load_chunk<DSL, SL>(p, sm, q_beg, min(DELTA_CHUNK, n), h, h, e0);
@@ -935,8 +988,9 @@ __global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p
             float qs4[4] = {0.f, 0.f, 0.f, 0.f};      // four sums in turn: short chains of dependent adds
 #pragma unroll
             for (int i = 0; i < DSL / 4; ++i) {
-                const float4 g4 = gr[i], k4 = kr[i], q4 = qr[i];
-                if (READ_FIRST) {
+                const float4 g4 = gr[i], k4 = kr[i];
+                const float4 q4 = read_out ? qr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (READ_FIRST && read_out) {
                     qs4[0] = fmaf(q4.x, S[4 * i], qs4[0]);
                     qs4[1] = fmaf(q4.y, S[4 * i + 1], qs4[1]);
                     qs4[2] = fmaf(q4.z, S[4 * i + 2], qs4[2]);
@@ -946,7 +1000,7 @@ __global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p
                 S[4 * i + 1] = fmaf(-g4.y, S[4 * i + 1], S[4 * i + 1]);
                 S[4 * i + 2] = fmaf(-g4.z, S[4 * i + 2], S[4 * i + 2]);
                 S[4 * i + 3] = fmaf(-g4.w, S[4 * i + 3], S[4 * i + 3]);
-                if (!READ_FIRST) {
+                if (!READ_FIRST && read_out) {
                     qs4[0] = fmaf(q4.x, S[4 * i], qs4[0]);
                     qs4[1] = fmaf(q4.y, S[4 * i + 1], qs4[1]);
                     qs4[2] = fmaf(q4.z, S[4 * i + 2], qs4[2]);
@@ -957,11 +1011,13 @@ __global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p
                 S[4 * i + 2] = fmaf(k4.z, val, S[4 * i + 2]);
                 S[4 * i + 3] = fmaf(k4.w, val, S[4 * i + 3]);
             }
-            float qS = (qs4[0] + qs4[1]) + (qs4[2] + qs4[3]);
+            if (read_out) {
+                float qS = (qs4[0] + qs4[1]) + (qs4[2] + qs4[3]);
 #pragma unroll
-            for (int o = 1; o < SL; o <<= 1) qS += __shfl_xor_sync(0xffffffffu, qS, o);
-            if (slice == 0 && e < E)
-                p.out[(size_t)(q_beg + c0 + tt) * ((size_t)p.H * E) + (size_t)h * E + e] = fmaf(bs[DELTA_CHUNK + tt], val, qS);
+                for (int o = 1; o < SL; o <<= 1) qS += __shfl_xor_sync(0xffffffffu, qS, o);
+                if (slice == 0 && e < E)
+                    p.out[(size_t)(q_beg + c0 + tt) * ((size_t)p.H * E) + (size_t)h * E + e] = fmaf(bs[DELTA_CHUNK + tt], val, qS);
+            }
         };
         if (nc == DELTA_CHUNK) {
 #pragma unroll
@@ -970,38 +1026,57 @@ __global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p
             for (int tt = 0; tt < nc; ++tt) token(tt);
         }
     }
-    if (st) {
+    // the request's state is left by the block that walked the sequence's last tokens; a segment before it leaves its own
+    float* leave = (j == n_segs - 1) ? st : (PART == 1 ? g.state + ((seg_first + j) * p.H + h) * (size_t)D * E : nullptr);
+    if (leave) {
 #pragma unroll
         for (int i = 0; i < DSL; ++i) {
             const int d = slice * DSL + i;
-            if (d < D && e < E) st[(size_t)d * E + e] = S[i];
+            if (d < D && e < E) leave[(size_t)d * E + e] = S[i];
         }
     }
 }
 
-template <int DSL, int SL>
-static cudaError_t launch_decay(const DeltaParams& p, int n_seqs, bool read_first, cudaStream_t s) {
+template <int DSL, int SL, bool READ_FIRST, int PART>
+static cudaError_t launch_decay_part(const DeltaParams& p, const DecaySegments& g, int n_seqs, cudaStream_t s) {
     using Sh = DeltaShape<DSL, SL>;
     const size_t smem = 2 * (size_t)Sh::BUF * sizeof(float);
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<DSL, SL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(decay_scan_kernel<DSL, SL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<DSL, SL, READ_FIRST, PART>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    dim3 grid(n_seqs, p.H, ceil_div(p.E, Sh::COLS));
-    if (read_first) return llmk_launch(decay_scan_kernel<DSL, SL, true>, grid, dim3(DELTA_THREADS), smem, s, true, p);
-    return llmk_launch(decay_scan_kernel<DSL, SL, false>, grid, dim3(DELTA_THREADS), smem, s, true, p);
+    dim3 grid(PART == 0 ? n_seqs : n_seqs * g.max_segs, p.H, ceil_div(p.E, Sh::COLS));
+    return llmk_launch(decay_scan_kernel<DSL, SL, READ_FIRST, PART>, grid, dim3(DELTA_THREADS), smem, s, true, p, g);
 }
+
+template <int DSL, int SL>
+static cudaError_t launch_decay(const DeltaParams& p, const DecaySegments& g, int n_seqs, bool read_first, cudaStream_t s) {
+    if (!g.state) {
+        return read_first ? launch_decay_part<DSL, SL, true, 0>(p, g, n_seqs, s) : launch_decay_part<DSL, SL, false, 0>(p, g, n_seqs, s);
+    }
+    cudaError_t e = read_first ? launch_decay_part<DSL, SL, true, 1>(p, g, n_seqs, s) : launch_decay_part<DSL, SL, false, 1>(p, g, n_seqs, s);
+    if (e != cudaSuccess) return e;
+    return read_first ? launch_decay_part<DSL, SL, true, 2>(p, g, n_seqs, s) : launch_decay_part<DSL, SL, false, 2>(p, g, n_seqs, s);
+}
+
+// Steps of DECAY_SEGMENTS_MIN_TOKENS token rows and more, of at most DECAY_SEGMENTS_MAX_SEQS sequences, are walked in
+// segments when the caller gives scratch for them: as many as fill the SMs once and the scratch holds, of 64 tokens at
+// least.
+constexpr int DECAY_SEGMENTS_MIN_TOKENS = 256, DECAY_SEGMENTS_MAX_SEQS = 8;
 
 // q, k [n_tokens, H * D] and v [n_tokens, H * E] of the storage dtype (rows q_ld, k_ld, v_ld apart); decay float32
 // [n_tokens, H * D]: the pre-activations, rewritten in place; bias float32 [H * D] or null; bonus float32 [H * D] or null;
 // qkv_buf float32 scratch [n_tokens, 2 H D + H E]; dots float32 scratch [n_tokens, 2 H]; state float32, S [H][D][E] of slot
 // s at state + s * state_ld; out float32 [n_tokens, H * E].  read_first != 0: a token reads the state before its own
-// decay and key enter it (its own key counts `bonus` times); else after both.
+// decay and key enter it (its own key counts `bonus` times); else after both.  seg_scratch (float32, seg_floats values, or
+// null): room for the segments' states and decay products; without it every sequence is walked whole.  *launches (or
+// null) receives the number of kernels launched.
 LLMK_EXPORT int llmk_decay_scan(float* out, const void* q, long long q_ld, const void* k, long long k_ld, const void* v, long long v_ld,
                                 float* decay, const float* bias, const float* bonus, float* qkv_buf, float* dots, float* state,
                                 long long state_ld, const int* cu_q, const int* state_slots, int n_seqs, int n_tokens, int H, int D,
-                                int E, int mode, float tau, float q_scale, int read_first, int dtype, void* stream) {
+                                int E, int mode, float tau, float q_scale, int read_first, float* seg_scratch, long long seg_floats,
+                                int* launches, int dtype, void* stream) {
+    if (launches) *launches = 0;
     if (n_seqs <= 0 || n_tokens <= 0) return LLMK_OK;
     if (H <= 0 || D <= 0 || D > 256 || E <= 0) LLMK_FAIL("decay_scan: heads %d, key width %d (at most 256), value width %d", H, D, E);
     if (mode != DECAY_SIGMOID_POW && mode != DECAY_EXP_EXP) LLMK_FAIL("decay_scan: unknown decay form %d", mode);
@@ -1026,11 +1101,42 @@ LLMK_EXPORT int llmk_decay_scan(float* out, const void* q, long long q_ld, const
     p.state = state; p.state_ld = state_ld; p.cu_q = cu_q; p.state_slots = state_slots;
     p.H = H; p.G = H; p.D = D; p.E = E;
     p.vec_ok = (D % 4 == 0 && E % 4 == 0 && host_aligned16(qkv_buf) && host_aligned16(decay)) ? 1 : 0;
+    DecaySegments g;
+    g.state = nullptr; g.decay = nullptr; g.seg_len = 0; g.max_segs = 1;
+    if (seg_scratch && n_tokens >= DECAY_SEGMENTS_MIN_TOKENS && n_seqs <= DECAY_SEGMENTS_MAX_SEQS) {
+        // As many segments as fill the SMs once: however the step's rows are shared out among its sequences, a pass runs
+        // about (segments - 1) x heads x column tiles blocks, and a block that waits for a place costs a whole segment's
+        // time.  Two segments gain nothing (each pass walks one of them).  On a B200, one sequence of 2,048 tokens:
+        // 4 heads of 128 x 128 in 7 segments 216 us against 588 whole (8: 235, 4: 337), 16 heads of 64 x 64 in 4 segments
+        // 257 against 433 (7: 273); 32 heads of 64 x 64 fill the SMs as they are (466; 4 segments: 480).
+        static int sms = 0, smem_sm = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        }
+        const int dsl = D <= 64 ? 4 : (D <= 128 ? 8 : 16), sl = D <= 32 ? 8 : 16;
+        const int stride = dsl == 4 ? 12 : dsl + 4, cols = 4 * (32 / sl);
+        const long long smem_block = 2LL * (DELTA_CHUNK * (3 * sl * stride + cols) + 2 * DELTA_CHUNK) * 4 + 1024;
+        const long long places = (long long)sms * std::max<long long>(1, std::min<long long>(smem_sm / smem_block, 2048 / DELTA_THREADS));
+        const long long base = (long long)H * ceil_div(E, cols);
+        const long long per_seg = (long long)H * ((long long)D * E + D);
+        long long segs = std::min<long long>(places / base + 1, seg_floats / (per_seg * n_seqs));
+        segs = std::min<long long>(segs, n_tokens / 64);
+        if (segs >= 3) {
+            g.seg_len = ceil_div(ceil_div(n_tokens, (int)segs), 16) * 16;
+            g.max_segs = ceil_div(n_tokens, g.seg_len);
+            g.state = seg_scratch;
+            g.decay = seg_scratch + (long long)n_seqs * g.max_segs * H * D * E;
+        }
+    }
     const bool rf = read_first != 0;
-    if (D <= 32) e = launch_decay<4, 8>(p, n_seqs, rf, s);
-    else if (D <= 64) e = launch_decay<4, 16>(p, n_seqs, rf, s);
-    else if (D <= 128) e = launch_decay<8, 16>(p, n_seqs, rf, s);
-    else e = launch_decay<16, 16>(p, n_seqs, rf, s);
+    if (D <= 32) e = launch_decay<4, 8>(p, g, n_seqs, rf, s);
+    else if (D <= 64) e = launch_decay<4, 16>(p, g, n_seqs, rf, s);
+    else if (D <= 128) e = launch_decay<8, 16>(p, g, n_seqs, rf, s);
+    else e = launch_decay<16, 16>(p, g, n_seqs, rf, s);
     LLMK_CHECK_LAUNCH_RC("decay_scan", e);
+    if (launches) *launches = g.state ? 3 : 2;
     return LLMK_OK;
 }

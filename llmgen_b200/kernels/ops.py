@@ -947,15 +947,24 @@ def token_shift_mix(out: torch.Tensor, x: torch.Tensor, mu: torch.Tensor, state:
                                          c_int(n_mix), c_int(dtype_code(x.dtype)), _stream()))
 
 
+def decay_scan_segment_floats(heads: int, dim: int, vdim: int) -> int:
+    """float32 values of the scratch that lets `decay_scan` walk long sequences in segments: 64 segments' states and
+    decay products (eight sequences of eight segments, or fewer of more)."""
+    return 64 * heads * (dim * vdim + dim)
+
+
 def decay_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, bias: Optional[torch.Tensor],
                bonus: Optional[torch.Tensor], state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int, heads: int,
-               dim: int, vdim: int, form: str, tau: float, q_scale: float, read_first: bool, qkv_buf: torch.Tensor, dots: torch.Tensor) -> None:
+               dim: int, vdim: int, form: str, tau: float, q_scale: float, read_first: bool, qkv_buf: torch.Tensor, dots: torch.Tensor,
+               segments: Optional[torch.Tensor] = None) -> None:
     """Linear attention with a decay per head and key channel over each sequence's new tokens (csrc/recurrent.cu).
     q, k [n, heads dim], v [n, heads vdim] of the storage dtype (any row stride); decay float32 [n, heads dim], the decays'
     pre-activations z, REWRITTEN; with b = `bias` (float32 [heads dim]) the decay is sigmoid(z + b)^(1/tau) ("sigmoid_pow")
     or exp(-exp(z + b)) ("exp_exp").  state float32 [slots, >= heads dim vdim]; out float32 [n, heads vdim].
     `read_first`: o = (S + diag(bonus) k v^T)^T q before S <- diag(a) S + k v^T; else o = S^T q after it.  q is multiplied
-    by `q_scale`.  `qkv_buf` float32 scratch [n, 2 heads dim + heads vdim], `dots` float32 scratch [n, 2 heads]."""
+    by `q_scale`.  `qkv_buf` float32 scratch [n, 2 heads dim + heads vdim], `dots` float32 scratch [n, 2 heads].
+    `segments` (float32, `decay_scan_segment_floats` values): with it, steps of some hundred token rows of a few sequences
+    walk each sequence in segments side by side (two launches) instead of token by token from its first to its last."""
     lib = build.load("recurrent")
     n = out.shape[0]
     if any(t.dtype != torch.float32 for t in (out, decay, state, qkv_buf, dots)) or q.dtype != k.dtype or q.dtype != v.dtype:
@@ -968,11 +977,16 @@ def decay_scan(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Ten
     for name, t in (("bias", bias), ("bonus", bonus)):
         if t is not None and (t.dtype != torch.float32 or t.numel() != heads * dim or not t.is_contiguous()):
             raise KernelError(f"decay_scan: {name} is float32 [heads, dim]")
+    if segments is not None and (segments.dtype != torch.float32 or not segments.is_contiguous()):
+        raise KernelError("decay_scan: the segments' scratch is a contiguous float32 array")
+    launched = c_int(0)
     _check(lib, lib.llmk_decay_scan(_ptr(out), _ptr(q), c_longlong(_row_stride(q)), _ptr(k), c_longlong(_row_stride(k)), _ptr(v),
                                     c_longlong(_row_stride(v)), _ptr(decay), _ptr(bias), _ptr(bonus), _ptr(qkv_buf), _ptr(dots), _ptr(state),
                                     c_longlong(_row_stride(state)), _ptr(cu_q), _ptr(state_slots), c_int(n_seqs), c_int(n), c_int(heads),
                                     c_int(dim), c_int(vdim), c_int(DECAY_FORMS[form]), c_float(tau), c_float(q_scale),
-                                    c_int(1 if read_first else 0), c_int(dtype_code(q.dtype)), _stream()), 2)
+                                    c_int(1 if read_first else 0), _ptr(segments), c_longlong(segments.numel() if segments is not None else 0),
+                                    ctypes.byref(launched), c_int(dtype_code(q.dtype)), _stream()), 0)
+    _Counter.launches += launched.value
 
 
 # ------------------------------------------------------------------------------ linear attention

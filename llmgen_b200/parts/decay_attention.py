@@ -12,9 +12,11 @@ from .spec import VECTOR, ChannelDecayAttentionSpec, TokenShiftDecaySpec, Weight
 
 
 def _scan_buffers(ws, T: int, H: int, D: int, E: int):
-    """The recurrence kernel's scratch: a float32 row [q | k | v] per token and two numbers per token and head."""
+    """The recurrence kernel's scratch: a float32 row [q | k | v] per token, two numbers per token and head, and the
+    states of the segments in which long sequences are walked."""
     return (ws.buffer("decay_scan_qkv", T, 2 * H * D + H * E, torch.float32),
-            ws.buffer("decay_scan_dots", T, 2 * H, torch.float32))
+            ws.buffer("decay_scan_dots", T, 2 * H, torch.float32),
+            ws.flat("decay_scan_segments", ops.decay_scan_segment_floats(H, D, E), torch.float32))
 
 
 class ChannelDecayAttention(Mixer):
@@ -69,7 +71,7 @@ class ChannelDecayAttention(Mixer):
         elem = 2 if self.dtype == torch.bfloat16 else 4
         hd, he = self.H * self.D, self.H * self.E
         return tokens * (self.w_in.shape[0] * elem + (3 * hd + 2 * he + 2 * self.H) * 4 + he * elem + self.spec.hidden_size * elem) \
-            + ops.SLICED_PRODUCT_BYTES
+            + ops.SLICED_PRODUCT_BYTES + 4 * ops.decay_scan_segment_floats(self.H, self.D, self.E)
 
     def forward(self, ctx, x, cache: LayerCache):
         T, ws = ctx.n_tokens, ctx.workspace
@@ -78,10 +80,10 @@ class ChannelDecayAttention(Mixer):
         # the decays' up-projection leaves in float32: what follows it (sigmoid, logarithm, power) is 32-bit arithmetic
         decay = linear(packed[:, self.a_off:], self.w_decay, ws.buffer("cda_decay", T, H * D, torch.float32))
         o = ws.buffer("cda_o", T, H * E, torch.float32)
-        qkv_buf, dots = _scan_buffers(ws, T, H, D, E)
+        qkv_buf, dots, segments = _scan_buffers(ws, T, H, D, E)
         ops.decay_scan(o, packed[:, :self.k_off], packed[:, self.k_off:self.v_off], packed[:, self.v_off:self.g_off], decay,
                        self.decay_bias, None, cache.state, ctx.cu_q, ctx.state_slots, ctx.n_seqs, H, D, E, "sigmoid_pow",
-                       float(self.spec.tau), float(D) ** -0.5, False, qkv_buf, dots)
+                       float(self.spec.tau), float(D) ** -0.5, False, qkv_buf, dots, segments)
         # one gain vector for all heads: every (token, head) is a row of the norm; the gate's rows lie in the packed product
         y = ws.buffer("cda_y", T, H * E, self.dtype)
         ops.gated_rmsnorm(y.view(T * H, E), o.view(T * H, E), packed[:, self.g_off:self.a_off], self.norm_gain, self.norm_eps,
@@ -140,7 +142,8 @@ class TokenShiftDecay(Mixer):
     def workspace_bytes(self, tokens: int) -> int:
         elem = 2 if self.dtype == torch.bfloat16 else 4
         hd, W = self.H * self.D, self.spec.hidden_size
-        return tokens * ((5 * W + 5 * hd + 2 * self.spec.decay_rank + W) * elem + (5 * hd + 2 * self.H) * 4) + ops.SLICED_PRODUCT_BYTES
+        return tokens * ((5 * W + 5 * hd + 2 * self.spec.decay_rank + W) * elem + (5 * hd + 2 * self.H) * 4) + ops.SLICED_PRODUCT_BYTES \
+            + 4 * ops.decay_scan_segment_floats(self.H, self.D, self.D)
 
     def forward(self, ctx, x, cache: LayerCache):
         T, ws = ctx.n_tokens, ctx.workspace
@@ -157,9 +160,9 @@ class TokenShiftDecay(Mixer):
         # the decays' up-projection leaves in float32: what follows it (two exponentials) is 32-bit arithmetic
         decay = linear(low_act, self.w_up, ws.buffer("tsd_decay", T, H * D, torch.float32))
         o = ws.buffer("tsd_o", T, H * D, torch.float32)
-        qkv_buf, dots = _scan_buffers(ws, T, H, D, D)
+        qkv_buf, dots, segments = _scan_buffers(ws, T, H, D, D)
         ops.decay_scan(o, r, k, v, decay, self.decay_bias, self.bonus, cache.state, ctx.cu_q, ctx.state_slots, ctx.n_seqs, H, D, D,
-                       "exp_exp", 1.0, 1.0, True, qkv_buf, dots)
+                       "exp_exp", 1.0, 1.0, True, qkv_buf, dots, segments)
         y = ws.buffer("tsd_y", T, H * D, self.dtype)
         ops.gated_rmsnorm(y.view(T * H, D), o.view(T * H, D), gate, self.out_gain, float(self.spec.eps), gate_form="silu", heads=H,
                           gains_per_head=True)

@@ -68,7 +68,8 @@ class GatedMLP(FeedForward):
         elem = 2 if self.dtype == torch.bfloat16 else 4
         return tokens * (2 * F + F + H) * elem + 2 * ops.SLICED_PRODUCT_BYTES
 
-    def forward(self, ctx, x):
+    def hidden(self, ctx, x):
+        """act(x Wg^T) * (x Wu^T), [T, F] of the storage dtype, by the fused product that fits the step's rows."""
         T = x.shape[0]
         F, H = self.spec.intermediate_size, self.spec.hidden_size
         ws = ctx.workspace
@@ -80,7 +81,7 @@ class GatedMLP(FeedForward):
             else:
                 gate_up = linear_sliced(ws, "ffn_gate_up", x, self.w_gate_up, self.dtype)
                 ops.act_rows(act, gate_up, "gelu_tanh_glu", group=self.group)
-            return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype)
+            return act
         gated = self.group == GATE_UP_GROUP and F % GATE_UP_GROUP == 0 and gated_product_usable(x, self.w_gate_up)
         cluster = min(ops.gemm_skinny_cluster_splits(T, 2 * F, H), 4) if gated and T <= ops.SKINNY_CLUSTER_MAX_ROWS else 1
         if gated and T <= ops.ROWS8_GATED_BEST_ROWS and ops.gemm_rows8_gated_usable(x, self.w_gate_up):
@@ -98,7 +99,10 @@ class GatedMLP(FeedForward):
         else:
             gate_up = linear_sliced(ws, "ffn_gate_up", x, self.w_gate_up, self.dtype)
             ops.silu_mul(act, gate_up, group=self.group)
-        return linear_sliced(ws, "ffn_out", act, self.w_down, self.dtype)
+        return act
+
+    def forward(self, ctx, x):
+        return linear_sliced(ctx.workspace, "ffn_out", self.hidden(ctx, x), self.w_down, self.dtype)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

@@ -7,7 +7,7 @@ from ..kernels import ops
 from .base import FeedForward
 from .linear import GEMM_MODULES, linear, linear_sliced
 from .registry import register_feed_forward
-from .spec import VECTOR, ClampedExpertSpec, DenseMLPSpec, GatedExpertSpec, RoutedMLPSpec, WeightDecl
+from .spec import VECTOR, ClampedExpertSpec, DenseMLPSpec, GatedExpertSpec, GatedMLPSpec, RoutedMLPSpec, WeightDecl
 
 
 class DenseMLP(FeedForward):
@@ -72,7 +72,9 @@ class RoutedMLP(FeedForward):
                  gated activation follows row-wise, and a second grouped launch runs down
       float32    (and operands TMA refuses) tiles of 16 rows through `moe_experts`, float32 sums on the CUDA cores
 
-    The shared expert is two of the framework's own products with the same activation between them."""
+    The shared expert is two of the framework's own products with the same activation between them; a plain
+    silu-gated one is the dense gated feed-forward's first half (`GatedMLP.hidden`: the activation in the product's
+    epilogue) and one more product."""
 
     step_arrays_follow_shapes = True
 
@@ -89,7 +91,7 @@ class RoutedMLP(FeedForward):
 
     @staticmethod
     def kernel_modules(spec):
-        return ("moe", "rowwise") + GEMM_MODULES
+        return ("moe", "rowwise", "elementwise") + GEMM_MODULES
 
     def __init__(self, spec: RoutedMLPSpec, weights, dtype, device):
         first = spec.experts[0]
@@ -116,8 +118,13 @@ class RoutedMLP(FeedForward):
         if self.grouped:
             self.w_gate_up = torch.cat([self.w_gate, self.w_up], dim=1).contiguous()
             self.w_gate = self.w_up = None
-        self.shared_gate_up = self.shared_down = None
-        if spec.shared is not None:
+        self.shared_gate_up = self.shared_down = self.shared_mlp = None
+        if isinstance(spec.shared, GatedExpertSpec):
+            from .mlp import GatedMLP
+            sh = spec.shared
+            self.shared_mlp = GatedMLP(GatedMLPSpec(H, sh.intermediate_size, sh.gate_proj, sh.up_proj, sh.down_proj, sh.activation),
+                                       weights, dtype, device)
+        elif spec.shared is not None:
             self.shared_gate_up = torch.cat([weights.device_tensor(spec.shared.gate_proj, dtype, device, keep=False),
                                              weights.device_tensor(spec.shared.up_proj, dtype, device, keep=False)], dim=0).contiguous()
             self.shared_down = weights.device_tensor(spec.shared.down_proj, dtype, device)
@@ -127,6 +134,8 @@ class RoutedMLP(FeedForward):
         H = self.spec.hidden_size
         slots = tokens * self.top
         shared = tokens * (3 * self.spec.shared.intermediate_size + H) * elem if self.spec.shared is not None else 0
+        if self.shared_mlp is not None:
+            shared += self.shared_mlp.workspace_bytes(tokens)
         rows = slots + ops.MOE_GROUPED_TILE * min(self.E, slots) if self.grouped else slots
         return rows * (3 * self.F + 2 * H) * 4 + tokens * H * 4 + shared + 16 * (rows + self.E) + 2 * ops.SLICED_PRODUCT_BYTES
 
@@ -161,7 +170,9 @@ class RoutedMLP(FeedForward):
             ops.moe_experts(rows, y, self.w_down, None, order, slot_weight, tile_expert, tile_start, tile_rows, n_slots, top,
                             first=False, weight_on_input=spec.weight_on_input)
         shared_out = None
-        if spec.shared is not None:
+        if self.shared_mlp is not None:
+            shared_out = linear(self.shared_mlp.hidden(ctx, x), self.shared_mlp.w_down, ws.buffer("moe_shared_out", T, H, self.dtype))
+        elif spec.shared is not None:
             Fs = spec.shared.intermediate_size
             gate_up = linear_sliced(ws, "moe_shared_gate_up", x, self.shared_gate_up, self.dtype)
             act = ws.buffer("moe_shared_act", T, Fs, self.dtype)

@@ -242,8 +242,6 @@ def test_attn_prep_refuses_what_it_cannot_do(ops):
     # a pairing or a per-head norm that no kernel implements is refused by name, not computed as another
     x16 = torch.zeros(1, 48, dtype=torch.float32, device="cuda")
     with pytest.raises(ops.KernelError, match="pairing"):
-        ops.attn_prep(x16, None, None, None, None, None, None, None, None, 1, 1, 16, 0, 4, 0.0, pairing="interleaved")
-    with pytest.raises(ops.KernelError, match="pairing"):
         ops.attn_prep(x16, None, None, None, None, None, None, None, None, 1, 1, 16, 0, 4, 0.0, pairing="spiral")
     with pytest.raises(ops.KernelError, match="normalises heads"):
         ops.attn_prep(x16, None, None, None, None, None, None, None, None, 1, 1, 16, 0, 4, 0.0, head_norm="layernorm")
