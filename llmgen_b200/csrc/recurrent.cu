@@ -1059,13 +1059,115 @@ static cudaError_t launch_decay(const DeltaParams& p, const DecaySegments& g, in
     return read_first ? launch_decay_part<DSL, SL, true, 2>(p, g, n_seqs, s) : launch_decay_part<DSL, SL, false, 2>(p, g, n_seqs, s);
 }
 
+// Steps of a few token rows (single decoded tokens, short portions): one launch.  A block per (sequence, head, 64 value
+// columns) prepares a token's q, k and 1 - a itself (the arithmetic of `decay_prep`), keeps its part of S in registers
+// over the sequence's tokens (a thread holds every fourth key channel of one column, so a row of S is read by
+// consecutive threads), and adds up the four partial read-outs of a column through shared memory.
+constexpr int DECAY_STEP_MAX_TOKENS = 32;
+
+template <typename T, bool READ_FIRST, int NR>
+__global__ void __launch_bounds__(256) decay_step_kernel(float* __restrict__ out, const T* __restrict__ q, long long q_ld,
+                                                         const T* __restrict__ k, long long k_ld, const T* __restrict__ v, long long v_ld,
+                                                         const float* __restrict__ z, const float* __restrict__ bias,
+                                                         const float* __restrict__ bonus, float* __restrict__ state, long long state_ld,
+                                                         const int* __restrict__ cu_q, const int* __restrict__ state_slots, int H, int D,
+                                                         int E, int mode, float inv_tau, float q_scale) {
+    __shared__ float sq[4 * NR], sk[4 * NR], sc[4 * NR];
+    __shared__ float partial[4][64];
+    __shared__ float warp_dots[8];
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int ce = threadIdx.x & 63, part = threadIdx.x >> 6, e = blockIdx.z * 64 + ce;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int q_beg = cu_q[s], n = cu_q[s + 1] - q_beg;
+    if (n <= 0) return;
+    const int slot = state_slots[s];
+    float* st = slot >= 0 ? state + (size_t)slot * state_ld + (size_t)h * D * E : nullptr;
+    float S[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        const int d = part + 4 * i;
+        S[i] = (st && d < D && e < E) ? st[(size_t)d * E + e] : 0.f;
+    }
+    for (int t = 0; t < n; ++t) {
+        const size_t row = (size_t)(q_beg + t);
+        float dot = 0.f;
+        for (int d = threadIdx.x; d < 4 * NR; d += 256) {
+            float qv = 0.f, kv = 0.f, c = 0.f;
+            if (d < D) {
+                const int i = h * D + d;
+                qv = to_float(q[row * q_ld + i]) * q_scale;
+                kv = to_float(k[row * k_ld + i]);
+                const float x = z[row * ((size_t)H * D) + i] + (bias ? bias[i] : 0.f);
+                const float log_a = mode == DECAY_SIGMOID_POW ? -softplusf_(-x) * inv_tau : -expf(x);
+                c = -expm1f(log_a);
+                dot = fmaf(qv * (bonus ? bonus[i] : 1.f), kv, dot);
+            }
+            sq[d] = qv;
+            sk[d] = kv;
+            sc[d] = c;
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) warp_dots[warp] = dot;
+        __syncthreads();
+        dot = ((warp_dots[0] + warp_dots[1]) + (warp_dots[2] + warp_dots[3])) + ((warp_dots[4] + warp_dots[5]) + (warp_dots[6] + warp_dots[7]));
+        const float val = e < E ? to_float(v[row * v_ld + (size_t)h * E + e]) : 0.f;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int d = part + 4 * i;
+            if (READ_FIRST) acc[i & 3] = fmaf(sq[d], S[i], acc[i & 3]);
+            S[i] = fmaf(-sc[d], S[i], S[i]);
+            if (!READ_FIRST) acc[i & 3] = fmaf(sq[d], S[i], acc[i & 3]);
+            S[i] = fmaf(sk[d], val, S[i]);
+        }
+        partial[part][ce] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        __syncthreads();
+        if (part == 0 && e < E) {
+            const float qS = (partial[0][ce] + partial[1][ce]) + (partial[2][ce] + partial[3][ce]);
+            out[row * ((size_t)H * E) + (size_t)h * E + e] = fmaf(dot, val, qS);
+        }
+        __syncthreads();      // the next token's q, k, 1 - a and partial sums go where this one's were read
+    }
+    if (st) {
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int d = part + 4 * i;
+            if (d < D && e < E) st[(size_t)d * E + e] = S[i];
+        }
+    }
+}
+
+template <typename T>
+static cudaError_t launch_decay_step(float* out, const void* q, long long q_ld, const void* k, long long k_ld, const void* v, long long v_ld,
+                                     const float* z, const float* bias, const float* bonus, float* state, long long state_ld,
+                                     const int* cu_q, const int* state_slots, int n_seqs, int H, int D, int E, int mode, float inv_tau,
+                                     float q_scale, bool read_first, cudaStream_t s) {
+    dim3 grid(n_seqs, H, ceil_div(E, 64));
+#define LLMK_DECAY_STEP(RF, NR)                                                                                                    \
+    return llmk_launch(decay_step_kernel<T, RF, NR>, grid, dim3(256), 0, s, true, out, (const T*)q, q_ld, (const T*)k, k_ld,      \
+                       (const T*)v, v_ld, z, bias, bonus, state, state_ld, cu_q, state_slots, H, D, E, mode, inv_tau, q_scale)
+    if (D <= 64) {
+        if (read_first) LLMK_DECAY_STEP(true, 16);
+        LLMK_DECAY_STEP(false, 16);
+    }
+    if (D <= 128) {
+        if (read_first) LLMK_DECAY_STEP(true, 32);
+        LLMK_DECAY_STEP(false, 32);
+    }
+    if (read_first) LLMK_DECAY_STEP(true, 64);
+    LLMK_DECAY_STEP(false, 64);
+#undef LLMK_DECAY_STEP
+}
+
 // Steps of DECAY_SEGMENTS_MIN_TOKENS token rows and more, of at most DECAY_SEGMENTS_MAX_SEQS sequences, are walked in
 // segments when the caller gives scratch for them: as many as fill the SMs once and the scratch holds, of 64 tokens at
 // least.
 constexpr int DECAY_SEGMENTS_MIN_TOKENS = 256, DECAY_SEGMENTS_MAX_SEQS = 8;
 
 // q, k [n_tokens, H * D] and v [n_tokens, H * E] of the storage dtype (rows q_ld, k_ld, v_ld apart); decay float32
-// [n_tokens, H * D]: the pre-activations, rewritten in place; bias float32 [H * D] or null; bonus float32 [H * D] or null;
+// [n_tokens, H * D]: the pre-activations, rewritten in place (left alone by steps of a few rows); bias float32 [H * D] or null; bonus float32 [H * D] or null;
 // qkv_buf float32 scratch [n_tokens, 2 H D + H E]; dots float32 scratch [n_tokens, 2 H]; state float32, S [H][D][E] of slot
 // s at state + s * state_ld; out float32 [n_tokens, H * E].  read_first != 0: a token reads the state before its own
 // decay and key enter it (its own key counts `bonus` times); else after both.  seg_scratch (float32, seg_floats values, or
@@ -1087,6 +1189,18 @@ LLMK_EXPORT int llmk_decay_scan(float* out, const void* q, long long q_ld, const
     const long long qkv_ld = 2LL * H * D + (long long)H * E;
     const float inv_tau = mode == DECAY_SIGMOID_POW ? 1.0f / tau : 1.0f;
     cudaError_t e;
+    if (dtype != LLMK_F32 && dtype != LLMK_BF16) LLMK_FAIL("decay_scan: unknown dtype %d", dtype);
+    if (n_tokens <= DECAY_STEP_MAX_TOKENS) {
+        if (dtype == LLMK_F32)
+            e = launch_decay_step<float>(out, q, q_ld, k, k_ld, v, v_ld, decay, bias, bonus, state, state_ld, cu_q, state_slots, n_seqs, H, D, E,
+                                         mode, inv_tau, q_scale, read_first != 0, s);
+        else
+            e = launch_decay_step<bf16>(out, q, q_ld, k, k_ld, v, v_ld, decay, bias, bonus, state, state_ld, cu_q, state_slots, n_seqs, H, D, E,
+                                        mode, inv_tau, q_scale, read_first != 0, s);
+        LLMK_CHECK_LAUNCH_RC("decay_step", e);
+        if (launches) *launches = 1;
+        return LLMK_OK;
+    }
     if (dtype == LLMK_F32)
         e = llmk_launch(decay_prep_kernel<float>, dim3(n_tokens), dim3(256), 0, s, true, qkv_buf, qkv_ld, decay, dots, (const float*)q, q_ld,
                         (const float*)k, k_ld, (const float*)v, v_ld, bias, bonus, H, D, E, mode, inv_tau, q_scale);

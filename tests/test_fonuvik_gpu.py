@@ -322,7 +322,7 @@ def test_a_model_folder_through_the_replay_program_and_the_command_line(tmp_path
     from llmgen_b200.engine.api import write_random_model
     from tests.util import ROOT
     cfg = fu.MIXED
-    folder = write_random_model(str(tmp_path / "model"), cfg, seed=12, sigma=0.1, sigma_norm=0.2)
+    folder = write_random_model(str(tmp_path / "model"), cfg, seed=13, sigma=0.1, sigma_norm=0.2)
     path = os.path.join(folder, "config.json")
     with open(path) as f:
         written = json.load(f)

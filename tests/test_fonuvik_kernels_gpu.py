@@ -79,7 +79,8 @@ def plain_decays(z, bias, form, tau):
 @pytest.mark.parametrize("H,D,E", [(2, 8, 12), (3, 40, 72), (1, 136, 8), (2, 64, 64), (1, 6, 10)])
 def test_decay_scan_carries_its_state_between_calls(H, D, E, form, read_first, dtype):
     """Both orders of a token's steps, key widths of every register layout, value widths beyond a block's columns and no
-    multiples of four; a second and third step after the first; a sequence without tokens or slot in the list."""
+    multiples of four; steps after the first, of a few rows (one launch that prepares and walks) and of more (two); a
+    sequence without tokens or slot in the list."""
     from llmgen_b200.kernels import ops
     tau, q_scale = 3.0, 0.7
     bias = rnd((H * D,), 5, 0.5) + (2.0 if form == "sigmoid_pow" else -2.0)
@@ -88,7 +89,7 @@ def test_decay_scan_carries_its_state_between_calls(H, D, E, form, read_first, d
     state[1] = 7.0
     S = {i: torch.zeros(H, D, E, dtype=torch.float64) for i in range(3)}
     segments = torch.empty(ops.decay_scan_segment_floats(H, D, E), device=DEV)
-    for step, lens, cu, slots in steps_of([5, 1, 19], [1, 2, 33], [17, 16, 1]):
+    for step, lens, cu, slots in steps_of([5, 1, 19], [1, 2, 33], [17, 16, 1], [1, 1, 1], [3, 1, 2]):
         n = sum(lens)
         q, k, v, z = decay_inputs(n + 2, H, D, E, 20 + 10 * step, dtype)
         out = torch.full((n + 2, H * E), 3.0, device=DEV)
