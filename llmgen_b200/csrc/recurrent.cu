@@ -590,17 +590,17 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 
 // One chunk's rows into shared memory: q, k, 1 - g as [CHUNK][SL slices][STRIDE] (the padding keeps the slices' 16-byte
 // reads on different banks), v as [CHUNK][COLS], then beta [CHUNK] and q . k [CHUNK].
-template <int DSL, int SL>
+template <int DSL, int SL, int WARPS = 4>
 struct DeltaShape {
     static constexpr int STRIDE = DSL == 4 ? 12 : DSL + 4;
     static constexpr int ROW = SL * STRIDE;
-    static constexpr int COLS = 4 * (32 / SL);
+    static constexpr int COLS = WARPS * (32 / SL);
     static constexpr int BUF = DELTA_CHUNK * (3 * ROW + COLS) + 2 * DELTA_CHUNK;
 };
 
-template <int DSL, int SL>
+template <int DSL, int SL, int WARPS = 4>
 __device__ __forceinline__ void delta_load_chunk(const DeltaParams& p, float* buf, int t_first, int nc, int h, int kvh, int e0) {
-    using Sh = DeltaShape<DSL, SL>;
+    using Sh = DeltaShape<DSL, SL, WARPS>;
     constexpr int ROW = Sh::ROW, COLS = Sh::COLS, STRIDE = Sh::STRIDE;
     float* qs = buf;
     float* ks = qs + DELTA_CHUNK * ROW;
@@ -610,7 +610,7 @@ __device__ __forceinline__ void delta_load_chunk(const DeltaParams& p, float* bu
     const int D = p.D, E = p.E, GD = p.G * p.D;
     if (p.vec_ok) {
         const int vecs = D / 4;
-        for (int idx = threadIdx.x; idx < nc * vecs; idx += DELTA_THREADS) {
+        for (int idx = threadIdx.x; idx < nc * vecs; idx += WARPS * 32) {
             const int tt = idx / vecs, d = (idx % vecs) * 4;
             const size_t t = (size_t)(t_first + tt);
             const int at = tt * ROW + (d / DSL) * STRIDE + d % DSL;
@@ -618,12 +618,12 @@ __device__ __forceinline__ void delta_load_chunk(const DeltaParams& p, float* bu
             cp_async16(ks + at, p.qkv + t * p.qkv_ld + GD + (size_t)kvh * D + d);
             cp_async16(gs + at, p.decay + t * ((size_t)p.H * D) + (size_t)h * D + d);
         }
-        for (int idx = threadIdx.x; idx < nc * (COLS / 4); idx += DELTA_THREADS) {
+        for (int idx = threadIdx.x; idx < nc * (COLS / 4); idx += WARPS * 32) {
             const int tt = idx / (COLS / 4), cc = (idx % (COLS / 4)) * 4;
             if (e0 + cc < E) cp_async16(vs + tt * COLS + cc, p.qkv + (size_t)(t_first + tt) * p.qkv_ld + 2 * GD + (size_t)h * E + e0 + cc);
         }
     } else {
-        for (int idx = threadIdx.x; idx < nc * D; idx += DELTA_THREADS) {
+        for (int idx = threadIdx.x; idx < nc * D; idx += WARPS * 32) {
             const int tt = idx / D, d = idx % D;
             const size_t t = (size_t)(t_first + tt);
             const int at = tt * ROW + (d / DSL) * STRIDE + d % DSL;
@@ -631,7 +631,7 @@ __device__ __forceinline__ void delta_load_chunk(const DeltaParams& p, float* bu
             ks[at] = p.qkv[t * p.qkv_ld + GD + (size_t)kvh * D + d];
             gs[at] = p.decay[t * ((size_t)p.H * D) + (size_t)h * D + d];
         }
-        for (int idx = threadIdx.x; idx < nc * COLS; idx += DELTA_THREADS) {
+        for (int idx = threadIdx.x; idx < nc * COLS; idx += WARPS * 32) {
             const int tt = idx / COLS, cc = idx % COLS;
             if (e0 + cc < E) vs[idx] = p.qkv[(size_t)(t_first + tt) * p.qkv_ld + 2 * GD + (size_t)h * E + e0 + cc];
         }
@@ -907,9 +907,16 @@ struct DecaySegments {
     int seg_len, max_segs;
 };
 
+// Whole sequences are walked by the delta rule's blocks of four warps (a token's chain is shortest with one warp a
+// scheduler).  Segments are walked by blocks of eight: twice the columns share a chunk's rows of q, k and 1 - a, the same
+// shared memory holds twice the warps an SM, and with every SM full that is worth more than the longer chain (one
+// sequence of 2,048 tokens, 8 heads of 128 x 128: 324 us against 346; 32 heads of 64 x 64: 370 against 466 whole).
+constexpr int decay_warps(int part) { return part == 0 ? 4 : 8; }
+
 template <int DSL, int SL, bool READ_FIRST, int PART>
-__global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p, DecaySegments g) {
-    using Sh = DeltaShape<DSL, SL>;
+__global__ void __launch_bounds__(decay_warps(PART) * 32, 3) decay_scan_kernel(DeltaParams p, DecaySegments g) {
+    constexpr int DECAY_WARPS = decay_warps(PART), DECAY_THREADS = DECAY_WARPS * 32;
+    using Sh = DeltaShape<DSL, SL, DECAY_WARPS>;
     constexpr int ROW = Sh::ROW, COLS = Sh::COLS, STRIDE = Sh::STRIDE, BUF = Sh::BUF;
     extern __shared__ __align__(16) float sm[];
     const int s = PART == 0 ? blockIdx.x : blockIdx.x / g.max_segs;
@@ -920,7 +927,7 @@ __global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p
     const int e = e0 + col;
     const int D = p.D, E = p.E;
     // channels beyond key_dim, and value columns beyond value_dim, hold zeros throughout (no decay: 1 - a = 0)
-    for (int i = threadIdx.x; i < 2 * BUF; i += DELTA_THREADS) sm[i] = 0.f;
+    for (int i = threadIdx.x; i < 2 * BUF; i += DECAY_THREADS) sm[i] = 0.f;
     pdl_launch_dependents();
     pdl_wait();
     int q_beg = p.cu_q[s], n = p.cu_q[s + 1] - q_beg;
@@ -961,7 +968,7 @@ __global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p
         }
     }
     if (PART == 1 && j > 0 && blockIdx.z == 0) {
-        for (int d = threadIdx.x; d < D; d += DELTA_THREADS) {
+        for (int d = threadIdx.x; d < D; d += DECAY_THREADS) {
             const float* c = p.decay + (size_t)q_beg * ((size_t)p.H * D) + (size_t)h * D + d;
             float sum = 0.f;
             for (int t = 0; t < n; ++t) sum += log1pf(-c[(size_t)t * ((size_t)p.H * D)]);
@@ -969,14 +976,14 @@ __global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p
         }
     }
     __syncthreads();
-    delta_load_chunk<DSL, SL>(p, sm, q_beg, min(DELTA_CHUNK, n), h, h, e0);
+    delta_load_chunk<DSL, SL, DECAY_WARPS>(p, sm, q_beg, min(DELTA_CHUNK, n), h, h, e0);
     int turn = 0;
     for (int c0 = 0; c0 < n; c0 += DELTA_CHUNK, turn ^= 1) {
         const int nc = min(DELTA_CHUNK, n - c0);
         cp_async_wait_all();
         __syncthreads();      // this chunk has arrived, and the chunk before is consumed by every warp
         if (c0 + DELTA_CHUNK < n)
-            delta_load_chunk<DSL, SL>(p, sm + (turn ^ 1) * BUF, q_beg + c0 + DELTA_CHUNK, min(DELTA_CHUNK, n - c0 - DELTA_CHUNK), h, h, e0);
+            delta_load_chunk<DSL, SL, DECAY_WARPS>(p, sm + (turn ^ 1) * BUF, q_beg + c0 + DELTA_CHUNK, min(DELTA_CHUNK, n - c0 - DELTA_CHUNK), h, h, e0);
         const float* buf = sm + turn * BUF;
         const float* vs = buf + 3 * DELTA_CHUNK * ROW;
         const float* bs = vs + DELTA_CHUNK * COLS;
@@ -1039,14 +1046,15 @@ __global__ void __launch_bounds__(DELTA_THREADS) decay_scan_kernel(DeltaParams p
 
 template <int DSL, int SL, bool READ_FIRST, int PART>
 static cudaError_t launch_decay_part(const DeltaParams& p, const DecaySegments& g, int n_seqs, cudaStream_t s) {
-    using Sh = DeltaShape<DSL, SL>;
+    constexpr int DECAY_WARPS = decay_warps(PART), DECAY_THREADS = DECAY_WARPS * 32;
+    using Sh = DeltaShape<DSL, SL, DECAY_WARPS>;
     const size_t smem = 2 * (size_t)Sh::BUF * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<DSL, SL, READ_FIRST, PART>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
     dim3 grid(PART == 0 ? n_seqs : n_seqs * g.max_segs, p.H, ceil_div(p.E, Sh::COLS));
-    return llmk_launch(decay_scan_kernel<DSL, SL, READ_FIRST, PART>, grid, dim3(DELTA_THREADS), smem, s, true, p, g);
+    return llmk_launch(decay_scan_kernel<DSL, SL, READ_FIRST, PART>, grid, dim3(DECAY_THREADS), smem, s, true, p, g);
 }
 
 template <int DSL, int SL>
@@ -1231,9 +1239,9 @@ LLMK_EXPORT int llmk_decay_scan(float* out, const void* q, long long q_ld, const
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         }
         const int dsl = D <= 64 ? 4 : (D <= 128 ? 8 : 16), sl = D <= 32 ? 8 : 16;
-        const int stride = dsl == 4 ? 12 : dsl + 4, cols = 4 * (32 / sl);
+        const int stride = dsl == 4 ? 12 : dsl + 4, cols = decay_warps(1) * (32 / sl);
         const long long smem_block = 2LL * (DELTA_CHUNK * (3 * sl * stride + cols) + 2 * DELTA_CHUNK) * 4 + 1024;
-        const long long places = (long long)sms * std::max<long long>(1, std::min<long long>(smem_sm / smem_block, 2048 / DELTA_THREADS));
+        const long long places = (long long)sms * std::max<long long>(1, std::min<long long>(smem_sm / smem_block, 2048 / (decay_warps(1) * 32)));
         const long long base = (long long)H * ceil_div(E, cols);
         const long long per_seg = (long long)H * ((long long)D * E + D);
         long long segs = std::min<long long>(places / base + 1, seg_floats / (per_seg * n_seqs));

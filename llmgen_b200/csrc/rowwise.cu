@@ -249,6 +249,37 @@ __global__ void gated_rmsnorm_kernel(T* __restrict__ out, const float* __restric
     }
 }
 
+// The same for short rows (a head's values): a warp a row, eight rows a block, no block-wide sum.
+template <typename T>
+__global__ void __launch_bounds__(256) gated_rmsnorm_warp_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ g,
+                                                                 const float* __restrict__ w, int n_rows, int H, long long ldg, float eps,
+                                                                 int gate_act, int w_rows, int heads) {
+    const size_t r = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (r >= (size_t)n_rows) return;
+    float rinv = 1.f;
+    if (w) {
+        float ss = 0.f;
+        for (int i = lane; i < H; i += 32) {
+            const float v = o[r * H + i];
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+        rinv = 1.0f / sqrtf(ss / (float)H + eps);
+    }
+    const size_t head = r % (size_t)heads;
+    const float* wr = w ? w + (head % (size_t)w_rows) * H : nullptr;
+    const T* gr = g + (r / (size_t)heads) * ldg + head * H;
+    for (int i = lane; i < H; i += 32) {
+        const float gv = to_float(gr[i]);
+        const float sg = 1.0f / (1.0f + expf(-gv));
+        const float gate = gate_act == GATE_SIGMOID ? sg : gate_act == GATE_SILU ? gv * sg : gv;
+        out[r * H + i] = from_float<T>(o[r * H + i] * rinv * (wr ? wr[i] : 1.f) * gate);
+    }
+}
+
 LLMK_EXPORT int llmk_gated_rmsnorm(void* out, const float* o, const void* g, const float* w, int n_rows, int H, long long ldg,
                                    float eps, int gate_act, int w_rows, int heads, int dtype, void* stream) {
     if (n_rows <= 0 || H <= 0) return LLMK_OK;
@@ -257,6 +288,15 @@ LLMK_EXPORT int llmk_gated_rmsnorm(void* out, const float* o, const void* g, con
     const int threads = H >= 2048 ? 512 : H >= 512 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
+    if (H <= 256 && n_rows >= 64 && (dtype == LLMK_F32 || dtype == LLMK_BF16)) {
+        const dim3 grid((unsigned)ceil_div(n_rows, 8));
+        if (dtype == LLMK_F32)
+            e = llmk_launch(gated_rmsnorm_warp_kernel<float>, grid, dim3(256), 0, s, true, (float*)out, o, (const float*)g, w, n_rows, H, ldg, eps, gate_act, w_rows, heads);
+        else
+            e = llmk_launch(gated_rmsnorm_warp_kernel<bf16>, grid, dim3(256), 0, s, true, (bf16*)out, o, (const bf16*)g, w, n_rows, H, ldg, eps, gate_act, w_rows, heads);
+        LLMK_CHECK_LAUNCH_RC("gated_rmsnorm", e);
+        return LLMK_OK;
+    }
     if (dtype == LLMK_F32)
         e = llmk_launch(gated_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, true, (float*)out, o, (const float*)g, w, H, ldg, eps, gate_act, w_rows, heads);
     else if (dtype == LLMK_BF16)
