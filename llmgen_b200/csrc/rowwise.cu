@@ -195,6 +195,55 @@ __global__ void act_rows_kernel(T* __restrict__ out, const void* __restrict__ x,
     }
 }
 
+// The gated forms over whole 16-byte vectors: a thread takes one vector of gates, the vector of ups beside it, and writes
+// one vector (rows that are no partial sums, column counts and strides in whole vectors).  The arithmetic is the scalar
+// kernel's.
+template <typename T>
+__global__ void __launch_bounds__(256) act_rows_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int n, int F, long long ld,
+                                                           int mode, float alpha, float limit, int group) {
+    constexpr int N = Vec16<T>::N;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int vecs = F / N;
+    const long long total = (long long)n * vecs;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const size_t r = (size_t)(i / vecs);
+        const int f = (int)(i % vecs) * N;
+        size_t gc, uc;
+        if (mode == ACT_CLAMPED_GLU) {
+            gc = r * ld + f;
+            uc = gc + F;
+        } else {
+            gc = r * ld + (size_t)(f / group) * 2 * group + f % group;
+            uc = gc + group;
+        }
+        Vec16<T> gv, uv, y;
+        gv.raw = *reinterpret_cast<const decltype(gv.raw)*>(x + gc);
+        uv.raw = *reinterpret_cast<const decltype(uv.raw)*>(x + uc);
+        float g[N], u[N], v[N];
+        gv.unpack(g);
+        uv.unpack(u);
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            if (mode == ACT_CLAMPED_GLU) {
+                const float gg = fminf(g[k], limit), uu = fminf(fmaxf(u[k], -limit), limit);
+                v[k] = gg / (1.0f + expf(-alpha * gg)) * (uu + 1.0f);
+            } else {
+                v[k] = (mode == ACT_SILU_GLU ? g[k] / (1.0f + expf(-g[k])) : gelu_tanh(g[k])) * u[k];
+            }
+        }
+        y.pack(v);
+        *reinterpret_cast<decltype(y.raw)*>(out + (size_t)r * F + f) = y.raw;
+    }
+}
+
+template <typename T>
+static bool act_rows_vec_ok(const void* out, const void* x, int F, long long ld, int mode, int splits, int group) {
+    constexpr int N = 16 / (int)sizeof(T);
+    const bool gated = mode == ACT_CLAMPED_GLU || mode == ACT_SILU_GLU || mode == ACT_GELU_TANH_GLU;
+    return gated && splits == 0 && F % N == 0 && group % N == 0 && ld % N == 0 && host_aligned16(out) && host_aligned16(x);
+}
+
 LLMK_EXPORT int llmk_act_rows(void* out, const void* x, int n, int F, long long ld, int mode, float alpha, float limit,
                               int splits, long long split_stride, int group, int dtype, void* stream) {
     if (n <= 0 || F <= 0) return LLMK_OK;
@@ -205,6 +254,18 @@ LLMK_EXPORT int llmk_act_rows(void* out, const void* x, int n, int F, long long 
     if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
+    if ((dtype == LLMK_BF16 && act_rows_vec_ok<bf16>(out, x, F, ld, mode, splits, group)) ||
+        (dtype == LLMK_F32 && act_rows_vec_ok<float>(out, x, F, ld, mode, splits, group))) {
+        const int N = dtype == LLMK_BF16 ? 8 : 4;
+        long long vblocks = ((long long)n * (F / N) + 255) / 256;
+        if (vblocks > device_sm_count() * 16) vblocks = device_sm_count() * 16;
+        if (dtype == LLMK_BF16)
+            e = llmk_launch(act_rows_vec_kernel<bf16>, dim3((unsigned)vblocks), dim3(256), 0, s, true, (bf16*)out, (const bf16*)x, n, F, ld, mode, alpha, limit, group);
+        else
+            e = llmk_launch(act_rows_vec_kernel<float>, dim3((unsigned)vblocks), dim3(256), 0, s, true, (float*)out, (const float*)x, n, F, ld, mode, alpha, limit, group);
+        LLMK_CHECK_LAUNCH_RC("act_rows", e);
+        return LLMK_OK;
+    }
     if (dtype == LLMK_F32)
         e = llmk_launch(act_rows_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, (float*)out, x, n, F, ld, mode, alpha, limit, splits, split_stride, group);
     else if (dtype == LLMK_BF16)
