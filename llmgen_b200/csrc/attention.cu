@@ -27,6 +27,7 @@
 // its parts are merged); an output gate, out <- out * sigmoid(gate) element by element, applied as the row is written;
 // a mask in blocks of `chunk` positions counted from the sequence's start: a query sees the keys at or before it that lie
 // in its own block, floor(k / chunk) = floor(q / chunk) (with key parts, the visible keys of a single token are what is split).
+#define LLMK_MODULE_NAME "attention"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

@@ -33,6 +33,7 @@
 // group's heads share K/V reads, three phases, partial (m, l, o) merged afterwards; here the merge
 // needs no second launch, any group size is taken (chunks of up to 8 heads), head_dim is 64 or
 // 128, and a window is cut into parts too.  Other head sizes use csrc/attention.cu.
+#define LLMK_MODULE_NAME "attention_decode"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

@@ -13,6 +13,7 @@
 // memory: 16-byte `cp.async` copies out of the pages into two buffers, the next tile on its way while this one is used.  Semantics as in csrc/attention.cu (which takes float32, single tokens in
 // parts, and every size this kernel refuses): query j of a portion sits at position ctx - q_len + j.
 // Taken: key width and value width 64 or 128 each.
+#define LLMK_MODULE_NAME "attention_mma"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

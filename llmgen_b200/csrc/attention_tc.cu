@@ -35,6 +35,7 @@
 // with an error and the caller uses the CUDA-core kernel (csrc/attention.cu).  The cache arrays must
 // hold finite values everywhere (slots never written are zero): masked keys enter the second MMA
 // with weight 0.  Every wait is bounded; a wait that gives up raises `*error_flag`.
+#define LLMK_MODULE_NAME "attention_tc"
 #include "common.cuh"
 #include "tcgen05.cuh"
 

@@ -17,6 +17,7 @@
 // Cache arrays are [page][kv_head][page_size][hd]
 // (src/memory/page_atten.zig:2) and slot = page * page_size + offset, slot < 0 = do not store.
 // cos/sin tables are float32 [max_positions, rot/2], computed on the host in float64.
+#define LLMK_MODULE_NAME "attn_prep"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

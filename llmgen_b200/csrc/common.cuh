@@ -12,6 +12,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <string>
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -150,6 +151,15 @@ inline bool llmk_pdl_enabled() {
     if (on < 0) {
         const char* e = getenv("LLMGEN_PDL");
         on = (e && e[0] == '0') ? 0 : 1;
+#ifdef LLMK_MODULE_NAME
+        // LLMGEN_PDL_OFF=name,name: the attribute off for the launches of these source files only (to find which
+        // launch a fault of ordering belongs to)
+        const char* off = getenv("LLMGEN_PDL_OFF");
+        if (off) {
+            const std::string list = std::string(",") + off + ",";
+            if (list.find(std::string(",") + LLMK_MODULE_NAME + ",") != std::string::npos) on = 0;
+        }
+#endif
     }
     return on != 0;
 }

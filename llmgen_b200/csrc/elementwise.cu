@@ -7,6 +7,7 @@
 // (src/backend/cuda/memory/memcpy.cu:58-67) and `silu_kernel` + `mul_kernel`
 // (src/backend/cuda/activation/silu_v1.cu:6-18, src/backend/cuda/arithmetic/mul_v1.cu:3-16).
 // The residual stream is float32 here, so the sum x + delta is never rounded to bfloat16.
+#define LLMK_MODULE_NAME "elementwise"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

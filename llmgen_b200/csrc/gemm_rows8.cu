@@ -19,6 +19,7 @@
 //
 // The reference streams weights with a GEMV kernel for one row and calls cublasGemmEx for more
 // (src/backend/cuda/linear/linear.cu:22-96).
+#define LLMK_MODULE_NAME "gemm_rows8"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

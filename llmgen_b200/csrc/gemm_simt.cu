@@ -8,6 +8,7 @@
 // (src/module/linear.zig:48-82, src/backend/cpu/linear.zig:7-28); the reference's own CUDA path
 // is a bfloat16 GEMV or cuBLAS (src/backend/cuda/linear/linear.cu:22-96) and has no float32
 // product.
+#define LLMK_MODULE_NAME "gemm_simt"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

@@ -26,6 +26,7 @@
 // The reference uses a one-warp-per-output-row GEMV for M <= 2 and cuBLAS above
 // (src/backend/cuda/linear/linear.cu:22-96); this kernel covers both ranges up to 256 rows.
 #include <string.h>
+#define LLMK_MODULE_NAME "gemm_skinny"
 #include "common.cuh"
 #include "tcgen05.cuh"
 

@@ -27,6 +27,7 @@
 // block still frees its tensor memory before it returns.
 //
 // The reference calls `cublasGemmEx` for this product (src/backend/cuda/linear/linear.cu:89-96).
+#define LLMK_MODULE_NAME "gemm_tc"
 #include "common.cuh"
 #include "tcgen05.cuh"
 

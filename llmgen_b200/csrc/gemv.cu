@@ -5,6 +5,7 @@
 // Same role as the reference's `gemv_kernel<M, OUT_F32>` (src/backend/cuda/linear/linear.cu:22-61:
 // one warp per output row, 16-byte weight loads, K % 8 == 0, M <= SV_GEMV_MAX_M = 2).  Here
 // M <= 4, an optional float32 output (logits) and an optional accumulate into C.
+#define LLMK_MODULE_NAME "gemv"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

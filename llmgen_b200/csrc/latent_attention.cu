@@ -20,6 +20,7 @@
 // Rotation: pairs (2i, 2i + 1) ("interleaved") or (i, i + rot/2) ("half"), by the angle whose cos / sin the tables
 // hold per position.  Positions, angles, norms, scores, softmax and all sums are float32; the cache and the
 // matrices have the storage dtype.
+#define LLMK_MODULE_NAME "latent_attention"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

@@ -24,6 +24,7 @@
 //
 // A sequence whose state slot is negative or that brings no tokens (the padding of a step laid out for replay) is
 // skipped.
+#define LLMK_MODULE_NAME "linear_attention"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

@@ -17,6 +17,7 @@
 // The weight multiplies the expert's input (mode "input") or its output (mode "output").
 // Gated activation: g' = min(g, L), u' = clamp(u, -L, L), y = g' sigmoid(alpha g') (u' + 1)   (L <= 0: no clamp),
 // or the plain gated unit y = g sigmoid(g) u.
+#define LLMK_MODULE_NAME "moe"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

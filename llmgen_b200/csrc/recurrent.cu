@@ -19,6 +19,7 @@
 // belong to no sequence and are skipped, sequences without tokens too, so every launch here follows from a step's shape.
 // Every state is float32; gates, decays, their logarithms and exponentials, unit norms and the recurrences are float32
 // arithmetic in both storage dtypes.  The arithmetic of a token does not depend on where a step was cut.
+#define LLMK_MODULE_NAME "recurrent"
 #include "common.cuh"
 #include <algorithm>
 

@@ -16,6 +16,7 @@
 //                   residual stream with the embedding's output
 //
 // Sums of squares, gains, the residual and the activations' arithmetic are float32 in both storage dtypes.
+#define LLMK_MODULE_NAME "rowwise"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()

@@ -16,6 +16,7 @@
 // row's last ticket takes the maximum of the candidates, writes the id and puts the ticket counter back
 // to zero.  Scratch: SPLIT keys a row, then one counter a row, which must be zero before the first
 // launch and is zero after every launch.  A row without any comparable score (all NaN) gives id 0.
+#define LLMK_MODULE_NAME "sampling"
 #include "common.cuh"
 
 LLMK_DEFINE_LAST_ERROR()
