@@ -49,6 +49,7 @@ struct AttnParams {
     float* part_o;
     float* part_ml;
     const void* gate;        // [tokens, nq * vd] of the storage type, rows `gate_stride` apart, or null
+    const float* sink_values;  // with `sink`: the sink's score per query head [nq]; null: 0 for every head
     long long q_stride, o_stride, gate_stride;
     int max_blocks, nq, nkv, hd, vd, page_size, window, num_parts, part_size, bq, gc, chunks, sink, chunk;
     float scale, softcap;
@@ -254,10 +255,12 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
             const T* g = p.gate ? static_cast<const T*>(p.gate) + tok * p.gate_stride + (size_t)head_of[i] * vd : nullptr;
             float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
             if (p.sink && l[i] > 0.f) {
-                // the sink's score is 0: with M = max(m, 0), weights are e^(s - M) / (l e^(m - M) + e^(-M))
-                const float M = fmaxf(m[i], 0.f);
+                // the sink's score is z (0 unless the heads have learned ones): with M = max(m, z), weights are
+                // e^(s - M) / (l e^(m - M) + e^(z - M))
+                const float z = p.sink_values ? p.sink_values[head_of[i]] : 0.f;
+                const float M = fmaxf(m[i], z);
                 const float w = expf(m[i] - M);
-                inv = w / (l[i] * w + expf(-M));
+                inv = w / (l[i] * w + expf(z - M));
             }
 #pragma unroll
             for (int j = 0; j < HDL; ++j) {
@@ -272,7 +275,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
 template <typename T>
 __global__ void attention_reduce_kernel(T* __restrict__ out, long long o_stride, const float* __restrict__ part_o,
                                         const float* __restrict__ part_ml, int n_rows, int nq, int hd,
-                                        int num_parts, int sink, const T* __restrict__ gate, long long gate_stride) {
+                                        int num_parts, int sink, const float* __restrict__ sink_values, const T* __restrict__ gate, long long gate_stride) {
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= n_rows) return;
@@ -280,11 +283,12 @@ __global__ void attention_reduce_kernel(T* __restrict__ out, long long o_stride,
     float M = -INFINITY;
     for (int pt = 0; pt < num_parts; ++pt)
         if (ml[2 * pt + 1] > 0.f) M = fmaxf(M, ml[2 * pt]);
-    if (sink && M > -INFINITY) M = fmaxf(M, 0.f);
+    const float z = (sink && sink_values) ? sink_values[row % nq] : 0.f;
+    if (sink && M > -INFINITY) M = fmaxf(M, z);
     float denom = 0.f;
     for (int pt = 0; pt < num_parts; ++pt)
         if (ml[2 * pt + 1] > 0.f) denom += expf(ml[2 * pt] - M) * ml[2 * pt + 1];
-    if (sink && denom > 0.f) denom += expf(-M);
+    if (sink && denom > 0.f) denom += expf(z - M);
     const float inv = denom > 0.f ? 1.0f / denom : 0.f;
     const size_t tok = (size_t)(row / nq), head = (size_t)(row % nq);
     T* o = out + tok * o_stride + head * hd;
@@ -340,8 +344,8 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
                                      int max_blocks, const int* ctx_len, const int* cu_q, const int* tile_seq,
                                      const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int hd,
                                      int page_size, int window, float scale, int num_parts, int part_size,
-                                     void* scratch, int vd, float softcap, int sink, const void* gate, long long gate_stride,
-                                     int chunk, int dtype, void* stream) {
+                                     void* scratch, int vd, float softcap, int sink, const float* sink_values, const void* gate,
+                                     long long gate_stride, int chunk, int dtype, void* stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return LLMK_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0) LLMK_FAIL("paged_attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
     if (hd <= 0 || hd > 512) LLMK_FAIL("paged_attention: head_dim %d must be positive, at most 512", hd);
@@ -361,7 +365,7 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
     p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
     p.q_stride = q_stride; p.o_stride = o_stride; p.max_blocks = max_blocks;
     p.nq = nq; p.nkv = nkv; p.hd = hd; p.vd = vd; p.page_size = page_size; p.window = window;
-    p.softcap = softcap; p.sink = sink ? 1 : 0; p.gate = gate; p.gate_stride = gate_stride; p.chunk = chunk;
+    p.softcap = softcap; p.sink = sink ? 1 : 0; p.sink_values = sink_values; p.gate = gate; p.gate_stride = gate_stride; p.chunk = chunk;
     p.num_parts = num_parts; p.part_size = part_size; p.scale = scale;
     p.part_o = (float*)scratch;
     p.part_ml = num_parts > 1 ? (float*)scratch + (size_t)n_tokens * nq * num_parts * vd : nullptr;
@@ -383,10 +387,10 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
         const int blocks = ceil_div(n_rows, warps);
         if (dtype == LLMK_F32)
             attention_reduce_kernel<float><<<blocks, warps * 32, 0, s>>>((float*)out, o_stride, p.part_o, p.part_ml, n_rows, nq, vd, num_parts,
-                                                                         p.sink, (const float*)gate, gate_stride);
+                                                                         p.sink, sink_values, (const float*)gate, gate_stride);
         else
             attention_reduce_kernel<bf16><<<blocks, warps * 32, 0, s>>>((bf16*)out, o_stride, p.part_o, p.part_ml, n_rows, nq, vd, num_parts,
-                                                                        p.sink, (const bf16*)gate, gate_stride);
+                                                                        p.sink, sink_values, (const bf16*)gate, gate_stride);
         LLMK_CHECK_LAUNCH("attention_reduce");
     }
     return LLMK_OK;

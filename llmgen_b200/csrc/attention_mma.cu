@@ -28,6 +28,7 @@ struct Params {
     const bf16* vcache;
     bf16* out;
     const bf16* gate;
+    const float* sink_values;     // with `sink`: the sink's score per query head [nq]; null: 0
     const int* block_tables;
     const int* ctx_len;
     const int* cu_q;
@@ -242,9 +243,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(Params p) {
         if (row >= nq_tile) continue;
         float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
         if (p.sink && l[r] > 0.f) {
-            const float M = fmaxf(m[r], 0.f);
+            const float z = p.sink_values ? p.sink_values[head] : 0.f;
+            const float M = fmaxf(m[r], z);
             const float w = expf(m[r] - M);
-            inv = w / (l[r] * w + expf(-M));
+            inv = w / (l[r] * w + expf(z - M));
         }
         const size_t tok = (size_t)(q_beg + q0 + row);
         bf16* dst = p.out + tok * p.o_stride + (size_t)head * VD;
@@ -289,7 +291,7 @@ LLMK_EXPORT int llmk_attention_mma_tile_queries(int nq, int nkv, int hd, int vd)
 LLMK_EXPORT int llmk_attention_mma(void* out, long long o_stride, const void* q, long long q_stride, const void* kcache,
                                    const void* vcache, const int* block_tables, int max_blocks, const int* ctx_len, const int* cu_q,
                                    const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv, int hd, int vd,
-                                   int page_size, int window, float scale, float softcap, int sink, const void* gate,
+                                   int page_size, int window, float scale, float softcap, int sink, const float* sink_values, const void* gate,
                                    long long gate_stride, int chunk, void* stream) {
     if (n_tiles <= 0) return LLMK_OK;
     if (llmk_attention_mma_tile_queries(nq, nkv, hd, vd) == 0)
@@ -300,7 +302,7 @@ LLMK_EXPORT int llmk_attention_mma(void* out, long long o_stride, const void* q,
     if (nq > 65535) LLMK_FAIL("attention_mma: grid too large");
     Params p;
     p.q = (const bf16*)q; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache; p.out = (bf16*)out;
-    p.gate = (const bf16*)gate; p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q;
+    p.gate = (const bf16*)gate; p.sink_values = sink_values; p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q;
     p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.q_stride = q_stride; p.o_stride = o_stride; p.gate_stride = gate_stride;
     p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.sink = sink ? 1 : 0; p.chunk = chunk > 0 ? chunk : 0;
     p.scale = scale; p.softcap = softcap;

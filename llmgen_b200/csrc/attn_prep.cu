@@ -552,3 +552,153 @@ LLMK_EXPORT int llmk_attn_prep(const void* qkv, long long row_stride, int splits
     LLMK_CHECK_LAUNCH_RC("attn_prep", e);
     return LLMK_OK;
 }
+
+// ------------------------------------------------------------------------------------------------ norms over whole projections
+// For layers whose q and k are normed over the whole projection (all heads of a token at once, gains of that size) and
+// whose values are rotated too.  x [n, ld] float32 holds [q | k | v] of a token (nq hd, nk hd, nk vd values): q and k are
+// divided by the root mean square of their whole row (eps inside the root) and multiplied by their gains, the first `rot`
+// values of each head are turned in half-split pairs (i, i + rot / 2) by the position's angles; v is turned over all of
+// its vd values in pairs (m, m + vd / 2) by angles of its own table (vcos / vsin [max_positions, vd / 2]; none: v as it is).
+// q goes to q_out, k and v to the cache at the token's slot (slot < 0: not stored).  A block per token.
+template <typename T>
+__global__ void attn_prep_rows_kernel(const float* __restrict__ x, long long ld, T* __restrict__ q_out, long long q_stride,
+                                      T* __restrict__ kcache, T* __restrict__ vcache, const int* __restrict__ positions,
+                                      const int* __restrict__ slots, const float* __restrict__ cos_tab,
+                                      const float* __restrict__ sin_tab, const float* __restrict__ vcos,
+                                      const float* __restrict__ vsin, const float* __restrict__ q_gain,
+                                      const float* __restrict__ k_gain, int nq, int nk, int nkv_cache, int hd, int vd, int rot,
+                                      int page_size, float eps) {
+    __shared__ float scratch[33];
+    const size_t t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* row = x + t * ld;
+    const int nQ = nq * hd, nK = nk * hd, nV = nk * vd;
+    const int pos = positions ? positions[t] : 0;
+    const int slot = slots ? slots[t] : -1;
+    const int half = rot / 2;
+    float ssq = 0.f, ssk = 0.f;
+    for (int i = threadIdx.x; i < nQ; i += blockDim.x) ssq = fmaf(row[i], row[i], ssq);
+    for (int i = threadIdx.x; i < nK; i += blockDim.x) ssk = fmaf(row[nQ + i], row[nQ + i], ssk);
+    ssq = block_sum(ssq, scratch);
+    ssk = nK > 0 ? block_sum(ssk, scratch) : 0.f;
+    const float rq = 1.0f / sqrtf(ssq / (float)max(nQ, 1) + eps), rk = 1.0f / sqrtf(ssk / (float)max(nK, 1) + eps);
+    for (int i = threadIdx.x; i < nQ + nK; i += blockDim.x) {
+        const bool is_q = i < nQ;
+        const int c = is_q ? i : i - nQ;
+        const int d = c % hd;
+        const float* g = is_q ? q_gain : k_gain;
+        const float r = is_q ? rq : rk;
+        float val = row[i] * r * (g ? g[c] : 1.f);
+        if (d < rot) {
+            const int other = d < half ? i + half : i - half;
+            const int oc = d < half ? c + half : c - half;
+            const float pv = row[other] * r * (g ? g[oc] : 1.f);
+            const int f = d < half ? d : d - half;
+            const float cs = cos_tab[(size_t)pos * half + f], sn = sin_tab[(size_t)pos * half + f];
+            val = d < half ? val * cs - pv * sn : val * cs + pv * sn;
+        }
+        if (is_q) {
+            q_out[t * q_stride + c] = from_float<T>(val);
+        } else if (slot >= 0 && kcache) {
+            const int kvh = c / hd;
+            kcache[(((size_t)(slot / page_size) * nkv_cache + kvh) * page_size + slot % page_size) * hd + d] = from_float<T>(val);
+        }
+    }
+    if (slot < 0 || !vcache) return;
+    const int vhalf = vd / 2;
+    for (int i = threadIdx.x; i < nV; i += blockDim.x) {
+        const int kvh = i / vd, d = i % vd;
+        float val = row[nQ + nK + i];
+        if (vcos) {
+            const float pv = row[nQ + nK + (d < vhalf ? i + vhalf : i - vhalf)];
+            const int f = d < vhalf ? d : d - vhalf;
+            const float cs = vcos[(size_t)pos * vhalf + f], sn = vsin[(size_t)pos * vhalf + f];
+            val = d < vhalf ? val * cs - pv * sn : val * cs + pv * sn;
+        }
+        vcache[(((size_t)(slot / page_size) * nkv_cache + kvh) * page_size + slot % page_size) * vd + d] = from_float<T>(val);
+    }
+}
+
+LLMK_EXPORT int llmk_attn_prep_rows(const float* x, long long ld, void* q_out, long long q_stride, void* kcache, void* vcache,
+                                    const int* positions, const int* slots, const float* cos_tab, const float* sin_tab,
+                                    const float* vcos, const float* vsin, const float* q_gain, const float* k_gain, int n_tokens,
+                                    int nq, int nk, int nkv_cache, int hd, int vd, int rot, int page_size, float eps, int dtype,
+                                    void* stream) {
+    if (n_tokens <= 0) return LLMK_OK;
+    if (nq <= 0 || nk < 0 || hd <= 0 || vd <= 0 || !q_out) LLMK_FAIL("attn_prep_rows: bad sizes (nq %d, nk %d, hd %d, vd %d)", nq, nk, hd, vd);
+    if (!cos_tab) rot = 0;
+    if (rot < 0 || rot > hd || rot % 2 != 0) LLMK_FAIL("attn_prep_rows: rotary width %d must be even and at most head_dim %d", rot, hd);
+    if (rot > 0 && (!sin_tab || !positions)) LLMK_FAIL("attn_prep_rows: rotary tables need sin and positions");
+    if (vcos && (!vsin || !positions || vd % 2 != 0)) LLMK_FAIL("attn_prep_rows: rotated values need sin, positions and an even width");
+    if (nk > 0 && (page_size <= 0 || nkv_cache < nk)) LLMK_FAIL("attn_prep_rows: bad cache geometry page_size=%d kv heads=%d", page_size, nkv_cache);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(attn_prep_rows_kernel<float>, dim3(n_tokens), dim3(256), 0, s, true, x, ld, (float*)q_out, q_stride, (float*)kcache,
+                        (float*)vcache, positions, slots, cos_tab, sin_tab, vcos, vsin, q_gain, k_gain, nq, nk, nkv_cache, hd, vd, rot,
+                        page_size, eps);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(attn_prep_rows_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, true, x, ld, (bf16*)q_out, q_stride, (bf16*)kcache,
+                        (bf16*)vcache, positions, slots, cos_tab, sin_tab, vcos, vsin, q_gain, k_gain, nq, nk, nkv_cache, hd, vd, rot,
+                        page_size, eps);
+    else
+        LLMK_FAIL("attn_prep_rows: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("attn_prep_rows", e);
+    return LLMK_OK;
+}
+
+// The attention's rows on their way to the output projection: each head's vd values turned back in pairs (m, m + vd / 2) by
+// minus the position's angles (vcos / vsin [max_positions, vd / 2]; none: as they are), then multiplied by sigmoid(gate[t, h]),
+// one number per head (gate rows `gate_stride` apart; none: no gate).  In place; a thread per pair.
+template <typename T>
+__global__ void unrotate_gate_kernel(T* __restrict__ o, long long o_stride, const T* __restrict__ gate, long long gate_stride,
+                                     const int* __restrict__ positions, const float* __restrict__ vcos,
+                                     const float* __restrict__ vsin, long long n, int nq, int vd) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int vhalf = vd / 2;
+    const long long total = n * nq * vhalf;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int m = (int)(i % vhalf);
+        const int h = (int)((i / vhalf) % nq);
+        const size_t t = (size_t)(i / ((long long)vhalf * nq));
+        T* p = o + t * o_stride + (size_t)h * vd;
+        float a = to_float(p[m]), b = to_float(p[m + vhalf]);
+        if (vcos) {
+            const int pos = positions[t];
+            const float cs = vcos[(size_t)pos * vhalf + m], sn = vsin[(size_t)pos * vhalf + m];
+            const float a2 = a * cs + b * sn, b2 = b * cs - a * sn;
+            a = a2;
+            b = b2;
+        }
+        if (gate) {
+            const float g = 1.0f / (1.0f + expf(-to_float(gate[t * gate_stride + h])));
+            a *= g;
+            b *= g;
+        }
+        p[m] = from_float<T>(a);
+        p[m + vhalf] = from_float<T>(b);
+    }
+}
+
+LLMK_EXPORT int llmk_unrotate_gate(void* o, long long o_stride, const void* gate, long long gate_stride, const int* positions,
+                                   const float* vcos, const float* vsin, int n_tokens, int nq, int vd, int dtype, void* stream) {
+    if (n_tokens <= 0) return LLMK_OK;
+    if (nq <= 0 || vd <= 0 || vd % 2 != 0) LLMK_FAIL("unrotate_gate: %d heads of %d values (an even width)", nq, vd);
+    if (vcos && (!vsin || !positions)) LLMK_FAIL("unrotate_gate: the tables need sin and positions");
+    long long blocks = ((long long)n_tokens * nq * (vd / 2) + 255) / 256;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32)
+        e = llmk_launch(unrotate_gate_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, true, (float*)o, o_stride, (const float*)gate,
+                        gate_stride, positions, vcos, vsin, (long long)n_tokens, nq, vd);
+    else if (dtype == LLMK_BF16)
+        e = llmk_launch(unrotate_gate_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, true, (bf16*)o, o_stride, (const bf16*)gate,
+                        gate_stride, positions, vcos, vsin, (long long)n_tokens, nq, vd);
+    else
+        LLMK_FAIL("unrotate_gate: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("unrotate_gate", e);
+    return LLMK_OK;
+}

@@ -1,0 +1,420 @@
+// Recurrent mixers whose gates read the current token only, and matrix memories that are read and written by rank-one
+// steps:
+//
+//   min_gru         S_t = (1 - z_t) S_(t-1) + z_t c_t per channel, z = sigmoid(.), c = u + 1/2 where u >= 0 and sigmoid(u)
+//                   below; out = S_t * silu(g_t)
+//   mlstm_gates     the log gates of a matrix memory with a running maximum, i = cap tanh(. / cap) and
+//                   f = logsigmoid(cap tanh(. / cap)) per token and head, with the token's own q . k
+//   mlstm_maxima    m_t = max(f_t + m_(t-1), i_t) along each sequence (m carried in the state, 0 for a fresh request) and
+//                   from it what the memory's step needs: exp(f + m_(t-1) - m_t), exp(i - m_t), exp(-m_t)
+//   delta_rule_prep the generalized delta rule's vectors per token and head: the decay w = exp(-c0 sigmoid(z + w0)), the unit
+//                   key u = k / sqrt(sum k^2 + unit_eps), the removal b = sigmoid(a + a0) u, and the dots b . r and k . r
+//   memory_scan     the memory S [key_dim, value_dim] per head over each sequence's new tokens, in two forms:
+//                     delta   S_t = diag(w) S - b (u^T S) + k v^T (both terms read the old S);  o = S_t^T r
+//                     mlstm   S_t = keep S + take k v^T, n_t = keep n + take k;
+//                             o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + den_eps)
+//                   With the old S the read-out is  o = (w r)^T S - (b . r)(u^T S) + (k . r) v  (delta) and
+//                   keep q^T S + take (k . q) v  (mlstm), so a token is one pass over its part of S: the dot products
+//                   first, then the update.
+//
+// A step's sequences are given as everywhere else: sequence s owns token rows [cu_q[s], cu_q[s+1]), its state lies in
+// slot state_slots[s] (-1: none; the sequence then starts from zeros and leaves nothing).  Rows beyond cu_q[n_seqs]
+// belong to no sequence and are skipped, sequences without tokens too, so every launch here follows from a step's shape.
+// States, gates, decays, their logarithms and exponentials, unit norms and the recurrences are float32 arithmetic in both
+// storage dtypes.  The arithmetic of a token does not depend on where a step was cut.
+#define LLMK_MODULE_NAME "memory_scan"
+#include "common.cuh"
+
+LLMK_DEFINE_LAST_ERROR()
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+// log(sigmoid(x)) = -softplus(-x)
+__device__ __forceinline__ float logsigmoidf_(float x) { return x < -20.f ? x : -log1pf(expf(-x)); }
+
+// ------------------------------------------------------------------------------------------------------- min_gru
+// A thread per (sequence, channel) walks the sequence's tokens.  zxg [n, 3C] float32: z, u and g side by side.
+template <typename T>
+__global__ void min_gru_kernel(T* __restrict__ out, const float* __restrict__ zxg, long long ld, const float* __restrict__ bz,
+                               const float* __restrict__ bx, float* __restrict__ state, long long state_ld,
+                               const int* __restrict__ cu_q, const int* __restrict__ state_slots, int C) {
+    const int s = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (c >= C) return;
+    const int q_beg = cu_q[s], n = cu_q[s + 1] - q_beg;
+    if (n <= 0) return;
+    const int slot = state_slots[s];
+    float S = slot >= 0 ? state[(size_t)slot * state_ld + c] : 0.f;
+    const float b_z = bz ? bz[c] : 0.f, b_x = bx ? bx[c] : 0.f;
+#pragma unroll 4
+    for (int j = 0; j < n; ++j) {
+        const float* row = zxg + (size_t)(q_beg + j) * ld;
+        const float z = sigmoidf_(row[c] + b_z);
+        const float u = row[C + c] + b_x;
+        const float g = row[2 * C + c];
+        const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+        S = fmaf(z, cand - S, S);                       // (1 - z) S + z cand
+        out[(size_t)(q_beg + j) * C + c] = from_float<T>(S * (g * sigmoidf_(g)));
+    }
+    if (slot >= 0) state[(size_t)slot * state_ld + c] = S;
+}
+
+// ------------------------------------------------------------------------------------------------------- mlstm gates
+// A warp per (token, head): gates[t, h] = (i, f, (q . k) q_scale, -).
+template <typename T>
+__global__ void mlstm_gates_kernel(float* __restrict__ gates, const T* __restrict__ q, long long ldq, const T* __restrict__ k,
+                                   long long ldk, const T* __restrict__ gi, long long ldi, const T* __restrict__ gf, long long ldf,
+                                   const float* __restrict__ bi, const float* __restrict__ bf, const int* __restrict__ cu_q,
+                                   int n_seqs, int n_rows, int H, int D, float cap, float q_scale) {
+    const int lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    pdl_launch_dependents();
+    pdl_wait();
+    if (w >= (long long)n_rows * H) return;
+    const int t = (int)(w / H), h = (int)(w % H);
+    if (t >= cu_q[n_seqs]) return;
+    const T* qr = q + (size_t)t * ldq + (size_t)h * D;
+    const T* kr = k + (size_t)t * ldk + (size_t)h * D;
+    float dot = 0.f;
+    for (int d = lane; d < D; d += 32) dot = fmaf(to_float(qr[d]), to_float(kr[d]), dot);
+    dot = warp_sum(dot);
+    if (lane == 0) {
+        const float xi = to_float(gi[(size_t)t * ldi + h]) + (bi ? bi[h] : 0.f);
+        const float xf = to_float(gf[(size_t)t * ldf + h]) + (bf ? bf[h] : 0.f);
+        float4 o;
+        o.x = cap * tanhf(xi / cap);
+        o.y = logsigmoidf_(cap * tanhf(xf / cap));
+        o.z = dot * q_scale;
+        o.w = 0.f;
+        reinterpret_cast<float4*>(gates)[(size_t)t * H + h] = o;
+    }
+}
+
+// A thread per (sequence, head) walks the tokens: gates[t, h] <- (keep, take, exp(-m_t), take (q . k)).
+__global__ void mlstm_maxima_kernel(float* __restrict__ gates, float* __restrict__ m_state, long long state_ld,
+                                    const int* __restrict__ cu_q, const int* __restrict__ state_slots, int n_seqs, int H) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (idx >= n_seqs * H) return;
+    const int s = idx / H, h = idx % H;
+    const int q_beg = cu_q[s], n = cu_q[s + 1] - q_beg;
+    if (n <= 0) return;
+    const int slot = state_slots[s];
+    float m = slot >= 0 ? m_state[(size_t)slot * state_ld + h] : 0.f;
+    float4* g = reinterpret_cast<float4*>(gates);
+    for (int j = 0; j < n; ++j) {
+        float4 v = g[(size_t)(q_beg + j) * H + h];
+        const float mn = fmaxf(v.y + m, v.x);
+        const float keep = expf(v.y + m - mn), take = expf(v.x - mn);
+        m = mn;
+        v.x = keep; v.y = take; v.w = take * v.z; v.z = expf(-mn);
+        g[(size_t)(q_beg + j) * H + h] = v;
+    }
+    if (slot >= 0) m_state[(size_t)slot * state_ld + h] = m;
+}
+
+// ------------------------------------------------------------------------------------------------------- delta rule prep
+// A block per token, a warp per head in turn.  aux[t] = [w | b | u] (H D each), dots[t, h] = (b . r, k . r).
+template <typename T>
+__global__ void delta_rule_prep_kernel(float* __restrict__ aux, float* __restrict__ dots, const T* __restrict__ r, long long ldr,
+                                       const T* __restrict__ k, long long ldk, const T* __restrict__ a, long long lda,
+                                       const float* __restrict__ decay, long long ldd, const float* __restrict__ a_bias,
+                                       const float* __restrict__ w_bias, const int* __restrict__ cu_q, int n_seqs, int H, int D,
+                                       float decay_scale, float unit_eps) {
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (t >= cu_q[n_seqs]) return;
+    const int HD = H * D;
+    float* wt = aux + (size_t)t * 3 * HD;
+    for (int h = warp; h < H; h += nwarps) {
+        const T* kr = k + (size_t)t * ldk + (size_t)h * D;
+        const T* rr = r + (size_t)t * ldr + (size_t)h * D;
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            const float kv = to_float(kr[d]);
+            ss = fmaf(kv, kv, ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss + unit_eps);
+        float br = 0.f, kdr = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            const int c = h * D + d;
+            const float kv = to_float(kr[d]), rv = to_float(rr[d]);
+            const float u = kv * inv;
+            const float b = sigmoidf_(to_float(a[(size_t)t * lda + c]) + (a_bias ? a_bias[c] : 0.f)) * u;
+            const float w = expf(-decay_scale * sigmoidf_(decay[(size_t)t * ldd + c] + (w_bias ? w_bias[c] : 0.f)));
+            wt[c] = w;
+            wt[HD + c] = b;
+            wt[2 * HD + c] = u;
+            br = fmaf(b, rv, br);
+            kdr = fmaf(kv, rv, kdr);
+        }
+        br = warp_sum(br);
+        kdr = warp_sum(kdr);
+        if (lane == 0) {
+            dots[((size_t)t * H + h) * 2] = br;
+            dots[((size_t)t * H + h) * 2 + 1] = kdr;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------- memory scan
+// A block per (tile of CT value columns, head, sequence); sixteen lanes share a column of S, lane j of them holding key
+// rows j, j + 16, ...  A chunk of TC tokens' vectors is staged in shared memory, then walked token by token.
+constexpr int LANES = 16;     // lanes that share a column
+constexpr int CT = 8;         // value columns a block
+constexpr int TC = 8;         // tokens a chunk
+enum { FORM_DELTA = 0, FORM_MLSTM = 1 };
+
+struct ScanParams {
+    float* out;               // [n, H E]
+    const void *r, *k, *v;    // storage type, rows ldr / ldk / ldv apart
+    long long ldr, ldk, ldv;
+    const float* aux;         // delta: [n, 3 H D] = w | b | u
+    const float* dots;        // delta: [n, H, 2] = (b . r, k . r); mlstm: [n, H, 4] = (keep, take, exp(-m), take (q . k) q_scale)
+    float* state;             // [slots, state_ld]: S [H, D, E], then (mlstm) n [H, D]
+    long long state_ld;
+    const int *cu_q, *state_slots;
+    int H, D, E;
+    float r_scale, den_eps;
+};
+
+template <typename T, int FORM, int DPL>
+__global__ void __launch_bounds__(LANES* CT) memory_scan_kernel(ScanParams p) {
+    extern __shared__ float sm[];
+    const int tile = blockIdx.x, h = blockIdx.y, s = blockIdx.z;
+    const int tid = threadIdx.x, l = tid % LANES, col = tid / LANES;
+    const int D = p.D, E = p.E, H = p.H;
+    const int e = tile * CT + col;
+    const bool live = e < E;
+    // per token in the chunk: r [D], k [D], (delta) w [D], b [D], u [D]; v [CT]; scalars [4]
+    const int vecs = FORM == FORM_DELTA ? 5 : 2;
+    const int per_tok = vecs * D + CT + 4;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int q_beg = p.cu_q[s], n = p.cu_q[s + 1] - q_beg;
+    if (n <= 0) return;
+    const int slot = p.state_slots[s];
+    float* Sg = slot >= 0 ? p.state + (size_t)slot * p.state_ld + (size_t)h * D * E : nullptr;
+    float* ng = (slot >= 0 && FORM == FORM_MLSTM) ? p.state + (size_t)slot * p.state_ld + (size_t)H * D * E + (size_t)h * D : nullptr;
+    float S[DPL], nv[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        const int d = l + LANES * i;
+        S[i] = (Sg && live && d < D) ? Sg[(size_t)d * E + e] : 0.f;
+        nv[i] = (ng && d < D) ? ng[d] : 0.f;
+    }
+    const T* rp = static_cast<const T*>(p.r);
+    const T* kp = static_cast<const T*>(p.k);
+    const T* vp = static_cast<const T*>(p.v);
+    const int HD = H * D;
+    for (int c0 = 0; c0 < n; c0 += TC) {
+        const int nt = min(TC, n - c0);
+        __syncthreads();
+        for (int i = tid; i < nt * per_tok; i += LANES * CT) {
+            const int j = i / per_tok, o = i % per_tok;
+            const size_t t = (size_t)(q_beg + c0 + j);
+            float val;
+            if (o < D) val = to_float(rp[t * p.ldr + (size_t)h * D + o]) * p.r_scale;
+            else if (o < 2 * D) val = to_float(kp[t * p.ldk + (size_t)h * D + (o - D)]);
+            else if (o < vecs * D) {
+                const int which = (o - 2 * D) / D, d = (o - 2 * D) % D;
+                val = p.aux[t * 3 * HD + (size_t)which * HD + (size_t)h * D + d];
+            } else if (o < vecs * D + CT) {
+                const int ee = tile * CT + (o - vecs * D);
+                val = ee < E ? to_float(vp[t * p.ldv + (size_t)h * E + ee]) : 0.f;
+            } else {
+                const int q = o - vecs * D - CT;
+                if (FORM == FORM_DELTA) val = q < 2 ? p.dots[(t * H + h) * 2 + q] : 0.f;
+                else val = p.dots[(t * H + h) * 4 + q];
+            }
+            sm[i] = val;
+        }
+        __syncthreads();
+        for (int j = 0; j < nt; ++j) {
+            const float* tk = sm + j * per_tok;
+            const float* r_ = tk;
+            const float* k_ = tk + D;
+            const float v_e = tk[vecs * D + col];
+            const float* sc = tk + vecs * D + CT;
+            if (FORM == FORM_DELTA) {
+                const float* w_ = tk + 2 * D;
+                const float* b_ = tk + 3 * D;
+                const float* u_ = tk + 4 * D;
+                float seen = 0.f, read = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) {
+                    const int d = l + LANES * i;
+                    if (d < D) {
+                        seen = fmaf(u_[d], S[i], seen);
+                        read = fmaf(w_[d] * r_[d], S[i], read);
+                    }
+                }
+#pragma unroll
+                for (int o = LANES / 2; o > 0; o >>= 1) {
+                    seen += __shfl_xor_sync(0xffffffffu, seen, o);
+                    read += __shfl_xor_sync(0xffffffffu, read, o);
+                }
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) {
+                    const int d = l + LANES * i;
+                    if (d < D) S[i] = fmaf(k_[d], v_e, fmaf(w_[d], S[i], -b_[d] * seen));
+                }
+                if (l == 0 && live) p.out[(size_t)(q_beg + c0 + j) * H * E + (size_t)h * E + e] = read - sc[0] * seen + sc[1] * v_e;
+            } else {
+                const float keep = sc[0], take = sc[1], em = sc[2], kq = sc[3];
+                float read = 0.f, nq = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) {
+                    const int d = l + LANES * i;
+                    if (d < D) {
+                        read = fmaf(r_[d], S[i], read);
+                        nq = fmaf(r_[d], nv[i], nq);
+                    }
+                }
+#pragma unroll
+                for (int o = LANES / 2; o > 0; o >>= 1) {
+                    read += __shfl_xor_sync(0xffffffffu, read, o);
+                    nq += __shfl_xor_sync(0xffffffffu, nq, o);
+                }
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) {
+                    const int d = l + LANES * i;
+                    if (d < D) {
+                        const float tk_d = take * k_[d];
+                        S[i] = fmaf(tk_d, v_e, keep * S[i]);
+                        nv[i] = fmaf(keep, nv[i], tk_d);
+                    }
+                }
+                if (l == 0 && live) {
+                    const float num = fmaf(keep, read, kq * v_e);
+                    const float den = fmaxf(fabsf(fmaf(keep, nq, kq)), em) + p.den_eps;
+                    p.out[(size_t)(q_beg + c0 + j) * H * E + (size_t)h * E + e] = num / den;
+                }
+            }
+        }
+    }
+    if (Sg && live) {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int d = l + LANES * i;
+            if (d < D) Sg[(size_t)d * E + e] = S[i];
+        }
+    }
+    if (ng && tile == 0 && col == 0) {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int d = l + LANES * i;
+            if (d < D) ng[d] = nv[i];
+        }
+    }
+}
+
+template <typename T, int FORM>
+int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t st) {
+    const int vecs = FORM == FORM_DELTA ? 5 : 2;
+    const size_t smem = (size_t)TC * (vecs * p.D + CT + 4) * sizeof(float);
+    const dim3 grid(ceil_div(p.E, CT), p.H, n_seqs), block(LANES * CT);
+    const int dpl = ceil_div(p.D, LANES);
+#define SCAN_CASE(N)                                                                                                       \
+    if (dpl <= N) {                                                                                                        \
+        static bool configured = false;                                                                                    \
+        if (!configured && smem > 48 * 1024) {                                                                             \
+            cudaError_t e = cudaFuncSetAttribute(memory_scan_kernel<T, FORM, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                 (int)(TC * (5 * 256 + CT + 4) * sizeof(float)));                          \
+            if (e != cudaSuccess) LLMK_FAIL("memory_scan: cannot raise shared memory: %s", cudaGetErrorString(e));        \
+            configured = true;                                                                                             \
+        }                                                                                                                  \
+        LLMK_CHECK_LAUNCH_RC("memory_scan", llmk_launch(memory_scan_kernel<T, FORM, N>, grid, block, smem, st, true, p)); \
+        return LLMK_OK;                                                                                                    \
+    }
+    SCAN_CASE(1) SCAN_CASE(2) SCAN_CASE(4) SCAN_CASE(8) SCAN_CASE(16)
+#undef SCAN_CASE
+    LLMK_FAIL("memory_scan: key width %d exceeds 256", p.D);
+}
+
+}  // namespace
+
+// out[t, c] = S_t * silu(g_t) with S_t = (1 - z) S_(t-1) + z cand over each sequence; zxg float32 [n, 3C] rows `ld` apart;
+// state [slots, >= C] float32 rows `state_ld` apart.
+LLMK_EXPORT int llmk_min_gru(void* out, const float* zxg, long long ld, const float* bz, const float* bx, float* state,
+                             long long state_ld, const int* cu_q, const int* state_slots, int n_seqs, int C, int dtype, void* stream) {
+    if (n_seqs <= 0 || C <= 0) return LLMK_OK;
+    const dim3 grid(ceil_div(C, 128), n_seqs), block(128);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == LLMK_F32)
+        LLMK_CHECK_LAUNCH_RC("min_gru", llmk_launch(min_gru_kernel<float>, grid, block, 0, st, true, (float*)out, zxg, ld, bz, bx, state,
+                                                    state_ld, cu_q, state_slots, C));
+    else
+        LLMK_CHECK_LAUNCH_RC("min_gru", llmk_launch(min_gru_kernel<bf16>, grid, block, 0, st, true, (bf16*)out, zxg, ld, bz, bx, state,
+                                                    state_ld, cu_q, state_slots, C));
+    return LLMK_OK;
+}
+
+// gates [n, H, 4] float32 <- (keep, take, exp(-m), take (q . k) q_scale) per token and head; m [slots, >= H] carried in the state.
+LLMK_EXPORT int llmk_mlstm_gates(float* gates, const void* q, long long ldq, const void* k, long long ldk, const void* gi, long long ldi,
+                                 const void* gf, long long ldf, const float* bi, const float* bf, float* m_state, long long state_ld,
+                                 const int* cu_q, const int* state_slots, int n_seqs, int n_rows, int H, int D, float cap, float q_scale,
+                                 int dtype, void* stream) {
+    if (n_seqs <= 0 || n_rows <= 0) return LLMK_OK;
+    if (!(cap > 0.f)) LLMK_FAIL("mlstm_gates: the gates' bound must be positive");
+    if (!host_aligned16(gates)) LLMK_FAIL("mlstm_gates: the gates' array must lie on a 16-byte boundary");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int warps = 8;
+    const dim3 grid(ceil_div(n_rows * H, warps)), block(warps * 32);
+    if (dtype == LLMK_F32)
+        LLMK_CHECK_LAUNCH_RC("mlstm_gates", llmk_launch(mlstm_gates_kernel<float>, grid, block, 0, st, true, gates, (const float*)q, ldq,
+                                                        (const float*)k, ldk, (const float*)gi, ldi, (const float*)gf, ldf, bi, bf, cu_q,
+                                                        n_seqs, n_rows, H, D, cap, q_scale));
+    else
+        LLMK_CHECK_LAUNCH_RC("mlstm_gates", llmk_launch(mlstm_gates_kernel<bf16>, grid, block, 0, st, true, gates, (const bf16*)q, ldq,
+                                                        (const bf16*)k, ldk, (const bf16*)gi, ldi, (const bf16*)gf, ldf, bi, bf, cu_q,
+                                                        n_seqs, n_rows, H, D, cap, q_scale));
+    LLMK_CHECK_LAUNCH_RC("mlstm_maxima", llmk_launch(mlstm_maxima_kernel, dim3(ceil_div(n_seqs * H, 64)), dim3(64), 0, st, true, gates,
+                                                     m_state, state_ld, cu_q, state_slots, n_seqs, H));
+    return LLMK_OK;
+}
+
+// aux [n, 3 H D] float32 = w | b | u and dots [n, H, 2] = (b . r, k . r) of the generalized delta rule.
+LLMK_EXPORT int llmk_delta_rule_prep(float* aux, float* dots, const void* r, long long ldr, const void* k, long long ldk, const void* a,
+                                     long long lda, const float* decay, long long ldd, const float* a_bias, const float* w_bias,
+                                     const int* cu_q, int n_seqs, int n_rows, int H, int D, float decay_scale, float unit_eps, int dtype,
+                                     void* stream) {
+    if (n_seqs <= 0 || n_rows <= 0) return LLMK_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int warps = H < 8 ? (H < 1 ? 1 : H) : 8;
+    const dim3 grid(n_rows), block(warps * 32);
+    if (dtype == LLMK_F32)
+        LLMK_CHECK_LAUNCH_RC("delta_rule_prep", llmk_launch(delta_rule_prep_kernel<float>, grid, block, 0, st, true, aux, dots,
+                                                            (const float*)r, ldr, (const float*)k, ldk, (const float*)a, lda, decay, ldd,
+                                                            a_bias, w_bias, cu_q, n_seqs, H, D, decay_scale, unit_eps));
+    else
+        LLMK_CHECK_LAUNCH_RC("delta_rule_prep", llmk_launch(delta_rule_prep_kernel<bf16>, grid, block, 0, st, true, aux, dots,
+                                                            (const bf16*)r, ldr, (const bf16*)k, ldk, (const bf16*)a, lda, decay, ldd,
+                                                            a_bias, w_bias, cu_q, n_seqs, H, D, decay_scale, unit_eps));
+    return LLMK_OK;
+}
+
+// The memory's walk over each sequence's new tokens (see the top of the file).  form 0: delta, 1: mlstm.
+LLMK_EXPORT int llmk_memory_scan(float* out, const void* r, long long ldr, const void* k, long long ldk, const void* v, long long ldv,
+                                 const float* aux, const float* dots, float* state, long long state_ld, const int* cu_q,
+                                 const int* state_slots, int n_seqs, int H, int D, int E, int form, float r_scale, float den_eps,
+                                 int dtype, void* stream) {
+    if (n_seqs <= 0) return LLMK_OK;
+    if (H <= 0 || D <= 0 || E <= 0 || D > 256) LLMK_FAIL("memory_scan: heads %d, key width %d (at most 256), value width %d", H, D, E);
+    if (form != FORM_DELTA && form != FORM_MLSTM) LLMK_FAIL("memory_scan: unknown form %d", form);
+    if (form == FORM_DELTA && !aux) LLMK_FAIL("memory_scan: the delta form needs its vectors");
+    ScanParams p;
+    p.out = out; p.r = r; p.k = k; p.v = v; p.ldr = ldr; p.ldk = ldk; p.ldv = ldv; p.aux = aux; p.dots = dots; p.state = state;
+    p.state_ld = state_ld; p.cu_q = cu_q; p.state_slots = state_slots; p.H = H; p.D = D; p.E = E; p.r_scale = r_scale; p.den_eps = den_eps;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == LLMK_F32)
+        return form == FORM_DELTA ? launch_scan<float, FORM_DELTA>(p, n_seqs, st) : launch_scan<float, FORM_MLSTM>(p, n_seqs, st);
+    return form == FORM_DELTA ? launch_scan<bf16, FORM_DELTA>(p, n_seqs, st) : launch_scan<bf16, FORM_MLSTM>(p, n_seqs, st);
+}

@@ -7,13 +7,16 @@
 //                   for layers that norm a sublayer's input as well as its output
 //   scaled_sum      out (float32) = a y + b y2, for consumers that take one array
 //   cast_rows       out = (T) in, float32 in
-//   act_rows        relu(x)^2, tanh(x), the clamped gated unit  g' s(alpha g') (u' + 1)  with g' = min(g, L), u' = clamp(u, -L, L),
+//   act_rows        relu(x)^2, tanh(x), gelu_tanh(x), the clamped gated unit  g' s(alpha g') (u' + 1)  with g' = min(g, L), u' = clamp(u, -L, L),
 //                   or the gated units gelu_tanh(g) u and silu(g) u
 //   gated_rmsnorm   out[r, :] = rmsnorm(o[r, :]) * w * sigmoid(g[r, :])   (or, without gains, o * sigmoid(g)); the gate may
 //                   pass silu instead, or enter as it is; the gains may differ between `w_rows` consecutive rows (heads)
 //   add_bias        y[r, :] += b, y an array of T or of float32, or the float32 slices of a product (the first slice takes it)
 //   concat_stream   out[r, :] = [ (T)(resid[r, :] + delta[r, :]) | (T) x0[r, :] ]: the operand of a product that mixes the
 //                   residual stream with the embedding's output
+//   stream_step     layers that keep several residual streams x_1 .. x_S per token (hyper-connections): one kernel ends a
+//                   sublayer, x_t <- sum_s mix[s, t] x_s + out[t] y, and begins the next, rmsnorm(sum_t in[t] x_t) * w
+//   stream_spread / stream_collapse   every stream = one row; one row = the sum of the streams
 //
 // Sums of squares, gains, the residual and the activations' arithmetic are float32 in both storage dtypes.
 #define LLMK_MODULE_NAME "rowwise"
@@ -161,7 +164,8 @@ LLMK_EXPORT int llmk_cast_rows(void* out, const float* in, long long n, int dtyp
 // mode 2: x [n, 2F] as in mode 1: out = gelu_tanh(gate) * up, gelu_tanh(z) = z / 2 (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
 // mode 3: out[r, f] = tanh(x[r, f]), x [n, F]
 // mode 4: x [n, 2F] as in mode 2 (groups too): out = silu(gate) * up
-enum { ACT_RELU2 = 0, ACT_CLAMPED_GLU = 1, ACT_GELU_TANH_GLU = 2, ACT_TANH = 3, ACT_SILU_GLU = 4 };
+// mode 5: out[r, f] = gelu_tanh(x[r, f]), x [n, F]
+enum { ACT_RELU2 = 0, ACT_CLAMPED_GLU = 1, ACT_GELU_TANH_GLU = 2, ACT_TANH = 3, ACT_SILU_GLU = 4, ACT_GELU_TANH = 5 };
 
 __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -182,6 +186,8 @@ __global__ void act_rows_kernel(T* __restrict__ out, const void* __restrict__ x,
             v = a * a;
         } else if (mode == ACT_TANH) {
             v = tanhf(load_sum<T>(x, r * ld + f, splits, split_stride));
+        } else if (mode == ACT_GELU_TANH) {
+            v = gelu_tanh(load_sum<T>(x, r * ld + f, splits, split_stride));
         } else if (mode == ACT_GELU_TANH_GLU || mode == ACT_SILU_GLU) {
             // gate and up alternate in groups of `group` columns (group = F: all gates, then all ups)
             const size_t gc = r * ld + (size_t)(f / group) * 2 * group + f % group;
@@ -250,7 +256,7 @@ LLMK_EXPORT int llmk_act_rows(void* out, const void* x, int n, int F, long long 
     if (n <= 0 || F <= 0) return LLMK_OK;
     if (group <= 0) group = F;
     if (F % group != 0) LLMK_FAIL("act_rows: groups of %d columns do not divide %d", group, F);
-    if (mode < ACT_RELU2 || mode > ACT_SILU_GLU) LLMK_FAIL("act_rows: unknown activation %d", mode);
+    if (mode < ACT_RELU2 || mode > ACT_GELU_TANH) LLMK_FAIL("act_rows: unknown activation %d", mode);
     long long blocks = ((long long)n * F + 255) / 256;
     if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
     cudaStream_t s = (cudaStream_t)stream;
@@ -428,5 +434,130 @@ LLMK_EXPORT int llmk_concat_stream(void* out, const float* resid, const void* de
     else
         LLMK_FAIL("concat_stream: unknown dtype %d", dtype);
     LLMK_CHECK_LAUNCH_RC("concat_stream", e);
+    return LLMK_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ several residual streams
+// streams [n, S, H] float32.  With y (an array of T, float32 slices, or a y + b y2): every stream is rewritten from all the old
+// ones, x_t <- sum_s mix[s * S + t] x_s + out_coef[t] y.  With next_in: normed[r, :] = rmsnorm(sum_t next_in[t] x_t) * next_gain
+// (the new streams), the input of the sublayer that follows.  Either half may be absent.  A block per token row.
+constexpr int MAX_STREAMS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(512) stream_step_kernel(float* __restrict__ streams, const void* __restrict__ y, int splits, long long split_stride,
+                                   const void* __restrict__ y2, int splits2, long long split_stride2, float a, float b,
+                                   const float* __restrict__ mix, const float* __restrict__ out_coef,
+                                   const float* __restrict__ next_in, const float* __restrict__ next_gain, float eps,
+                                   T* __restrict__ normed, int S, int H) {
+    extern __shared__ float srow[];  // H floats + 33 scratch + S * S + 2 * S coefficients
+    float* scratch = srow + H;
+    float* coef = scratch + 33;      // mix [S, S], out [S], in [S]
+    const size_t r = blockIdx.x;
+    for (int i = threadIdx.x; i < S * S + 2 * S; i += blockDim.x) {
+        float c = 0.f;
+        if (i < S * S) c = mix ? mix[i] : 0.f;
+        else if (i < S * S + S) c = out_coef ? out_coef[i - S * S] : 0.f;
+        else c = next_in ? next_in[i - S * S - S] : 0.f;
+        coef[i] = c;
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    __syncthreads();
+    float* xs = streams + r * S * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float x[MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < MAX_STREAMS; ++s)
+            if (s < S) x[s] = xs[(size_t)s * H + i];
+        if (y) {
+            float v = load_sum<T>(y, r * H + i, splits, split_stride);
+            if (y2) v = a * v + b * load_sum<T>(y2, r * H + i, splits2, split_stride2);
+            float nx[MAX_STREAMS];
+#pragma unroll
+            for (int t = 0; t < MAX_STREAMS; ++t) {
+                if (t < S) {
+                    float acc = coef[S * S + t] * v;
+#pragma unroll
+                    for (int s = 0; s < MAX_STREAMS; ++s)
+                        if (s < S) acc = fmaf(coef[s * S + t], x[s], acc);
+                    nx[t] = acc;
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < MAX_STREAMS; ++t)
+                if (t < S) {
+                    x[t] = nx[t];
+                    xs[(size_t)t * H + i] = nx[t];
+                }
+        }
+        if (next_in) {
+            float u = 0.f;
+#pragma unroll
+            for (int t = 0; t < MAX_STREAMS; ++t)
+                if (t < S) u = fmaf(coef[S * S + S + t], x[t], u);
+            srow[i] = u;
+            ss = fmaf(u, u, ss);
+        }
+    }
+    if (!next_in) return;
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) normed[r * H + i] = from_float<T>(srow[i] * rinv * next_gain[i]);
+}
+
+LLMK_EXPORT int llmk_stream_step(float* streams, const void* y, int splits, long long split_stride, const void* y2, int splits2,
+                                 long long split_stride2, float a, float b, const float* mix, const float* out_coef,
+                                 const float* next_in, const float* next_gain, float eps, void* normed, int n_rows, int S, int H,
+                                 int dtype, void* stream) {
+    if (n_rows <= 0) return LLMK_OK;
+    if (S <= 0 || S > MAX_STREAMS || H <= 0 || !streams) LLMK_FAIL("stream_step: %d streams (at most %d) of %d values", S, MAX_STREAMS, H);
+    if (y && (!mix || !out_coef)) LLMK_FAIL("stream_step: a sublayer's output needs the streams' coefficients");
+    if (next_in && (!next_gain || !normed)) LLMK_FAIL("stream_step: the next sublayer's input needs gains and a place");
+    const size_t smem = ((size_t)H + 33 + S * S + 2 * S) * sizeof(float);
+    if (smem > 200 * 1024) LLMK_FAIL("stream_step: a row of %d values does not fit shared memory", H);
+    const int threads = H >= 2048 ? 512 : H >= 512 ? 256 : 128;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (dtype == LLMK_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(stream_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = llmk_launch(stream_step_kernel<float>, dim3(n_rows), dim3(threads), smem, st, true, streams, y, splits, split_stride, y2, splits2,
+                        split_stride2, a, b, mix, out_coef, next_in, next_gain, eps, (float*)normed, S, H);
+    } else if (dtype == LLMK_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(stream_step_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = llmk_launch(stream_step_kernel<bf16>, dim3(n_rows), dim3(threads), smem, st, true, streams, y, splits, split_stride, y2, splits2,
+                        split_stride2, a, b, mix, out_coef, next_in, next_gain, eps, (bf16*)normed, S, H);
+    } else
+        LLMK_FAIL("stream_step: unknown dtype %d", dtype);
+    LLMK_CHECK_LAUNCH_RC("stream_step", e);
+    return LLMK_OK;
+}
+
+// collapse == 0: streams[r, s, :] = row[r, :] for every s.  collapse != 0: row[r, :] = sum_s streams[r, s, :].
+__global__ void stream_spread_kernel(float* __restrict__ streams, float* __restrict__ row, long long n, int S, int H, int collapse) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n * H; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / H;
+        const int c = (int)(i % H);
+        float* xs = streams + (size_t)r * S * H + c;
+        if (collapse) {
+            float acc = xs[0];
+            for (int s = 1; s < S; ++s) acc += xs[(size_t)s * H];
+            row[i] = acc;
+        } else {
+            const float v = row[i];
+            for (int s = 0; s < S; ++s) xs[(size_t)s * H] = v;
+        }
+    }
+}
+
+LLMK_EXPORT int llmk_stream_spread(float* streams, float* row, int n_rows, int S, int H, int collapse, void* stream) {
+    if (n_rows <= 0) return LLMK_OK;
+    if (S <= 0 || H <= 0) LLMK_FAIL("stream_spread: %d streams of %d values", S, H);
+    long long blocks = ((long long)n_rows * H + 255) / 256;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    LLMK_CHECK_LAUNCH_RC("stream_spread", llmk_launch(stream_spread_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, true,
+                                                      streams, row, (long long)n_rows, S, H, collapse));
     return LLMK_OK;
 }

@@ -102,6 +102,12 @@ class DecoderModel:
             ops.widen(x0, resid)
         delta = None
         ctx.normed_for = None
+        stream = resid
+        n_streams = int(getattr(self.spec, "residual_streams", 0) or 0)
+        if n_streams > 0:
+            # layers that keep several residual streams: every stream starts as the embedding's output
+            resid = ctx.workspace.buffer("residual_streams", T, n_streams * H, torch.float32)
+            ops.stream_spread(resid.view(T, n_streams, H), stream)
         order = self.spec.run_order
         for n, (item, cache, before) in enumerate(zip(order, caches, self.before)):
             if before is not None:
@@ -111,6 +117,11 @@ class DecoderModel:
             ctx.next_block = (self.layers[order[n + 1].layer] if n + 1 < len(order) and self.before[n + 1] is None else None)
             delta = self.layers[item.layer].forward(ctx, resid, delta, cache)
         ctx.next_block = None
+        if n_streams > 0:
+            if delta is not None:
+                raise ValueError("a model with residual streams is made of blocks that finish their own sums")
+            ops.stream_spread(resid.view(T, n_streams, H), stream, collapse=True)     # the stream is the sum of the streams
+            resid = stream
         return resid, delta
 
     def logits(self, ctx: StepContext, resid: torch.Tensor, delta: Optional[torch.Tensor],

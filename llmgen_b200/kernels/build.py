@@ -55,6 +55,7 @@ MODULES: Dict[str, List[str]] = {
     "latent_attention": [],
     "moe": [],
     "recurrent": [],
+    "memory_scan": [],
     "runtime": [],      # host code only: cache manager, scheduler, step arrays
 }
 

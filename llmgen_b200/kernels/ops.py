@@ -533,19 +533,26 @@ def attention_scratch_floats(n_tokens: int, nq: int, hd: int, num_parts: int) ->
     return 0 if num_parts <= 1 else n_tokens * nq * num_parts * (hd + 2)
 
 
+def _check_sinks(who: str, sink: bool, sink_values: Optional[torch.Tensor], nq: int) -> None:
+    if sink_values is not None and (not sink or sink_values.dtype != torch.float32 or sink_values.numel() != nq
+                                    or not sink_values.is_contiguous()):
+        raise KernelError(f"{who}: the sinks' scores are one float32 per query head, with `sink` set")
+
+
 def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
                     block_tables: torch.Tensor, max_blocks: int, ctx_len: torch.Tensor, cu_q: torch.Tensor,
                     tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, n_tokens: int, nq: int, nkv: int,
                     hd: int, page_size: int, window: int, scale: float, num_parts: int = 1, part_size: int = 0,
                     scratch: Optional[torch.Tensor] = None, vd: int = 0, softcap: float = 0.0, sink: bool = False,
-                    gate: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
+                    gate: Optional[torch.Tensor] = None, chunk: int = 0, sink_values: Optional[torch.Tensor] = None) -> None:
     """out[t, nq*vd] = causal GQA of q[t] over the paged cache (see csrc/attention.cu).  `vd`: the values' width where
     it differs from `hd`; `softcap` > 0 bounds the scores by softcap * tanh(s / softcap); `sink` adds exp(0) to the
-    softmax's denominator; `gate` [tokens, nq*vd] (storage dtype): the result is multiplied by sigmoid(gate); `chunk` > 0:
+    softmax's denominator (exp(sink_values[head]) with `sink_values`, float32 [nq]); `gate` [tokens, nq*vd] (storage dtype): the result is multiplied by sigmoid(gate); `chunk` > 0:
     a query sees the keys at or before it inside its own block of that many positions, counted from the sequence's start."""
     lib = build.load("attention")
     if gate is not None and gate.dtype != q.dtype:
         raise KernelError("paged_attention: the gate has the storage dtype")
+    _check_sinks("paged_attention", sink, sink_values, nq)
     if num_parts > 1:
         need = attention_scratch_floats(n_tokens, nq, vd or hd, num_parts)
         if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
@@ -555,8 +562,8 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: t
                                          _ptr(ctx_len), _ptr(cu_q), _ptr(tile_seq), _ptr(tile_q0), c_int(n_tiles),
                                          c_int(n_tokens), c_int(nq), c_int(nkv), c_int(hd), c_int(page_size),
                                          c_int(window), c_float(scale), c_int(num_parts), c_int(part_size),
-                                         _ptr(scratch), c_int(vd), c_float(softcap), c_int(1 if sink else 0), _ptr(gate),
-                                         c_longlong(_row_stride(gate) if gate is not None else 0), c_int(chunk),
+                                         _ptr(scratch), c_int(vd), c_float(softcap), c_int(1 if sink else 0), _ptr(sink_values),
+                                         _ptr(gate), c_longlong(_row_stride(gate) if gate is not None else 0), c_int(chunk),
                                          c_int(dtype_code(q.dtype)), _stream()),
            2 if num_parts > 1 else 1)
 
@@ -569,17 +576,19 @@ def attention_mma_tile_queries(nq: int, nkv: int, hd: int, vd: int) -> int:
 def attention_mma(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
                   max_blocks: int, ctx_len: torch.Tensor, cu_q: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor,
                   n_tiles: int, nq: int, nkv: int, hd: int, vd: int, page_size: int, window: int, scale: float,
-                  softcap: float = 0.0, sink: bool = False, gate: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
+                  softcap: float = 0.0, sink: bool = False, gate: Optional[torch.Tensor] = None, chunk: int = 0,
+                  sink_values: Optional[torch.Tensor] = None) -> None:
     """Prompt portions in bfloat16 with 32-bit softmax weights on the tensor cores (csrc/attention_mma.cu): the same
     result as `paged_attention` with these options, tiles of `attention_mma_tile_queries` queries."""
     lib = build.load("attention_mma")
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or (gate is not None and gate.dtype != torch.bfloat16):
         raise KernelError("attention_mma: bfloat16 only")
+    _check_sinks("attention_mma", sink, sink_values, nq)
     _check(lib, lib.llmk_attention_mma(_ptr(out), c_longlong(_row_stride(out)), _ptr(q), c_longlong(_row_stride(q)), _ptr(kcache),
                                        _ptr(vcache), _ptr(block_tables), c_int(max_blocks), _ptr(ctx_len), _ptr(cu_q), _ptr(tile_seq),
                                        _ptr(tile_q0), c_int(n_tiles), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), c_int(page_size),
-                                       c_int(window), c_float(scale), c_float(softcap), c_int(1 if sink else 0), _ptr(gate),
-                                       c_longlong(_row_stride(gate) if gate is not None else 0), c_int(chunk), _stream()))
+                                       c_int(window), c_float(scale), c_float(softcap), c_int(1 if sink else 0), _ptr(sink_values),
+                                       _ptr(gate), c_longlong(_row_stride(gate) if gate is not None else 0), c_int(chunk), _stream()))
 
 
 def attention_decode_set_cluster_merge(on: bool) -> None:
@@ -703,7 +712,7 @@ def sample(out_ids: torch.Tensor, logits: torch.Tensor, temps: torch.Tensor, see
 
 
 # ---------------------------------------------------------------------- rows of post-norm layers
-ACTIVATIONS = {"relu2": 0, "clamped_glu": 1, "gelu_tanh_glu": 2, "tanh": 3, "silu_glu": 4}
+ACTIVATIONS = {"relu2": 0, "clamped_glu": 1, "gelu_tanh_glu": 2, "tanh": 3, "silu_glu": 4, "gelu_tanh": 5}
 
 
 def _delta_args(y, dtype: torch.dtype):
@@ -782,7 +791,8 @@ def act_rows(out: torch.Tensor, x, activation: str, alpha: float = 1.0, limit: f
     """out[n, F] = relu(x)^2 ("relu2", x [n, F]) or the clamped gated unit of x [n, 2F] ("clamped_glu": gate in
     the first F columns, up in the last): g' = min(g, limit), u' = clamp(u, -limit, limit),
     out = g' sigmoid(alpha g') (u' + 1); or gelu_tanh(gate) * up / silu(gate) * up of x [n, 2F] ("gelu_tanh_glu", "silu_glu",
-    where `group` > 0 says that gate and up columns alternate in groups of that many); or tanh(x) ("tanh", x [n, F]).
+    where `group` > 0 says that gate and up columns alternate in groups of that many); or tanh(x) / the tanh form of gelu
+    ("tanh", "gelu_tanh", x [n, F]).
     `x` is an array or a `Partials`."""
     lib = build.load("rowwise")
     try:
@@ -845,6 +855,166 @@ def concat_stream(out: torch.Tensor, resid: torch.Tensor, delta, x0: torch.Tenso
     src, splits, stride = (None, 0, 0) if delta is None else _delta_args(delta, out.dtype)
     _check(lib, lib.llmk_concat_stream(_ptr(out), _ptr(resid), _ptr(src), _ptr(x0), c_int(n), c_int(H), c_int(splits),
                                        c_longlong(stride), c_int(dtype_code(out.dtype)), _stream()))
+
+
+# ------------------------------------------------------------------------- several residual streams
+MAX_STREAMS = 8
+
+
+def stream_step(streams: torch.Tensor, y, mix: Optional[torch.Tensor], out_coef: Optional[torch.Tensor], next_in: Optional[torch.Tensor],
+                next_gain: Optional[torch.Tensor], eps: float, normed: Optional[torch.Tensor], dtype: torch.dtype) -> None:
+    """One step of a layer that keeps S residual streams per token, `streams` float32 [n, S, H] (csrc/rowwise.cu).  With `y` (a
+    sublayer's output: an array of the storage dtype, a `Partials`, or a `WeightedPair` of two such): every stream is rewritten
+    from all the old ones, x_t <- sum_s mix[s, t] x_s + out_coef[t] y.  With `next_in`: normed [n, H] (storage dtype) =
+    rmsnorm(sum_t next_in[t] x_t) * next_gain over the new streams.  Either half may be left out."""
+    lib = build.load("rowwise")
+    if streams.dtype != torch.float32 or streams.dim() != 3 or not streams.is_contiguous():
+        raise KernelError("stream_step: the streams are a contiguous float32 [n, S, H] array")
+    n, S, H = streams.shape
+    if S > MAX_STREAMS:
+        raise KernelError(f"stream_step: at most {MAX_STREAMS} streams")
+    second, a, b = None, 1.0, 0.0
+    src, splits, stride, src2, splits2, stride2 = None, 0, 0, None, 0, 0
+    if y is not None:
+        if isinstance(y, WeightedPair):
+            y, second, a, b = y.first, y.second, y.a, y.b
+        src, splits, stride = _delta_args(y, dtype)
+        if second is not None:
+            src2, splits2, stride2 = _delta_args(second, dtype)
+        rows = y.rows if isinstance(y, Partials) else y.shape[0]
+        cols = y.cols if isinstance(y, Partials) else y.shape[1]
+        if rows != n or cols != H or mix is None or out_coef is None or mix.numel() != S * S or out_coef.numel() != S:
+            raise KernelError("stream_step: the sublayer's output is [n, H] and comes with mix [S, S] and out [S]")
+    for c in (mix, out_coef, next_in, next_gain):
+        if c is not None and (c.dtype != torch.float32 or not c.is_contiguous()):
+            raise KernelError("stream_step: coefficients and gains are contiguous float32")
+    if next_in is not None and (next_in.numel() != S or next_gain is None or next_gain.numel() != H or normed is None
+                                or normed.dtype != dtype or tuple(normed.shape) != (n, H) or not normed.is_contiguous()):
+        raise KernelError("stream_step: the next sublayer's input needs in [S], gains [H] and a place [n, H]")
+    _check(lib, lib.llmk_stream_step(_ptr(streams), _ptr(src), c_int(splits), c_longlong(stride), _ptr(src2), c_int(splits2),
+                                     c_longlong(stride2), c_float(a), c_float(b), _ptr(mix), _ptr(out_coef), _ptr(next_in),
+                                     _ptr(next_gain), c_float(eps), _ptr(normed), c_int(n), c_int(S), c_int(H),
+                                     c_int(dtype_code(dtype)), _stream()))
+
+
+def stream_spread(streams: torch.Tensor, row: torch.Tensor, collapse: bool = False) -> None:
+    """streams (float32 [n, S, H]) <- every stream a copy of row (float32 [n, H]); `collapse`: row <- the sum of the streams."""
+    lib = build.load("rowwise")
+    if streams.dtype != torch.float32 or row.dtype != torch.float32 or streams.dim() != 3 or not streams.is_contiguous() \
+            or not row.is_contiguous() or tuple(row.shape) != (streams.shape[0], streams.shape[2]):
+        raise KernelError("stream_spread: float32 [n, S, H] and [n, H], contiguous")
+    n, S, H = streams.shape
+    _check(lib, lib.llmk_stream_spread(_ptr(streams), _ptr(row), c_int(n), c_int(S), c_int(H), c_int(1 if collapse else 0), _stream()))
+
+
+# ------------------------------------------------------------ norms over whole projections, rotated values
+def attn_prep_rows(x: torch.Tensor, q_out: torch.Tensor, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
+                   positions: torch.Tensor, slots: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                   vcos: Optional[torch.Tensor], vsin: Optional[torch.Tensor], q_gain: Optional[torch.Tensor],
+                   k_gain: Optional[torch.Tensor], nq: int, nk: int, hd: int, vd: int, rot: int, page_size: int, eps: float) -> None:
+    """x float32 [n, >= nq hd + nk hd + nk vd] = [q | k | v] of each token: q and k divided by the root mean square of their whole
+    row and multiplied by gains of that size (`q_gain` [nq hd], `k_gain` [nk hd]), the first `rot` values of every head turned
+    in half-split pairs; v turned over all of its width by `vcos` / `vsin` [positions, vd / 2] (None: as it is).  q goes to
+    `q_out` (storage dtype), k and v to the paged cache (csrc/attn_prep.cu)."""
+    lib = build.load("attn_prep")
+    n = x.shape[0]
+    if x.dtype != torch.float32 or x.shape[1] < nq * hd + nk * (hd + vd) or q_out.shape[0] != n or q_out.shape[1] < nq * hd:
+        raise KernelError("attn_prep_rows: float32 rows [q | k | v] in, q of the storage dtype out")
+    for g, w in ((q_gain, nq * hd), (k_gain, nk * hd)):
+        if g is not None and (g.dtype != torch.float32 or g.numel() != w or not g.is_contiguous()):
+            raise KernelError("attn_prep_rows: gains are float32 over a whole projection")
+    if kcache is not None and kcache.dtype != q_out.dtype:
+        raise KernelError("attn_prep_rows: the cache has the storage dtype")
+    nkv_cache = kcache.shape[1] if kcache is not None else 0
+    _check(lib, lib.llmk_attn_prep_rows(_ptr(x), c_longlong(_row_stride(x)), _ptr(q_out), c_longlong(_row_stride(q_out)), _ptr(kcache),
+                                        _ptr(vcache), _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin), _ptr(vcos), _ptr(vsin),
+                                        _ptr(q_gain), _ptr(k_gain), c_int(n), c_int(nq), c_int(nk), c_int(nkv_cache), c_int(hd), c_int(vd),
+                                        c_int(rot), c_int(page_size), c_float(eps), c_int(dtype_code(q_out.dtype)), _stream()))
+
+
+def unrotate_gate(o: torch.Tensor, gate: Optional[torch.Tensor], positions: torch.Tensor, vcos: Optional[torch.Tensor],
+                  vsin: Optional[torch.Tensor], nq: int, vd: int) -> None:
+    """o [n, nq vd] in place: every head turned back by minus its position's angles (pairs (m, m + vd / 2), tables
+    [positions, vd / 2]; None: not turned), then multiplied by sigmoid(gate[t, head]), `gate` [n, nq] of o's dtype with any row
+    stride (None: no gate)."""
+    lib = build.load("attn_prep")
+    if o.shape[1] != nq * vd or (gate is not None and (gate.dtype != o.dtype or gate.shape[0] != o.shape[0] or gate.shape[1] != nq)):
+        raise KernelError("unrotate_gate: o is [n, nq vd], the gate [n, nq] of the same dtype")
+    _check(lib, lib.llmk_unrotate_gate(_ptr(o), c_longlong(_row_stride(o)), _ptr(gate), c_longlong(_row_stride(gate) if gate is not None else 0),
+                                       _ptr(positions), _ptr(vcos), _ptr(vsin), c_int(o.shape[0]), c_int(nq), c_int(vd),
+                                       c_int(dtype_code(o.dtype)), _stream()))
+
+
+# ------------------------------------------------------------ gates on the current token, matrix memories
+def min_gru(out: torch.Tensor, zxg: torch.Tensor, bias_z: Optional[torch.Tensor], bias_x: Optional[torch.Tensor], state: torch.Tensor,
+            cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int) -> None:
+    """out[t, c] (storage dtype) = S_t silu(g_t), S_t = (1 - z) S_(t-1) + z cand, z = sigmoid(zxg[t, c] + bias_z), u = zxg[t, C + c] +
+    bias_x, cand = u + 1/2 where u >= 0 else sigmoid(u), g = zxg[t, 2C + c]; zxg float32 [n, 3C]; state float32 [slots, >= C]
+    (csrc/memory_scan.cu)."""
+    lib = build.load("memory_scan")
+    n, C = out.shape
+    if zxg.dtype != torch.float32 or tuple(zxg.shape) != (n, 3 * C) or state.dtype != torch.float32 or state.shape[1] < C \
+            or not out.is_contiguous():
+        raise KernelError("min_gru: float32 [n, 3C] in, [n, C] out, float32 state rows of at least C")
+    _check(lib, lib.llmk_min_gru(_ptr(out), _ptr(zxg), c_longlong(_row_stride(zxg)), _ptr(bias_z), _ptr(bias_x), _ptr(state),
+                                 c_longlong(_row_stride(state)), _ptr(cu_q), _ptr(state_slots), c_int(n_seqs), c_int(C),
+                                 c_int(dtype_code(out.dtype)), _stream()))
+
+
+def mlstm_gates(gates: torch.Tensor, q: torch.Tensor, k: torch.Tensor, gi: torch.Tensor, gf: torch.Tensor, bias_i: Optional[torch.Tensor],
+                bias_f: Optional[torch.Tensor], m_state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int,
+                heads: int, dim: int, cap: float, q_scale: float) -> None:
+    """gates float32 [n, heads, 4] <- (keep, take, exp(-m_t), take (q . k) q_scale) of a matrix memory with a running maximum:
+    i = cap tanh((gi + bias_i) / cap), f = logsigmoid(cap tanh((gf + bias_f) / cap)), m_t = max(f + m_(t-1), i), keep = exp(f +
+    m_(t-1) - m_t), take = exp(i - m_t); m is carried in `m_state` (float32 [slots, >= heads]).  q, k [n, heads dim] and gi, gf
+    [n, heads] of the storage dtype with any row stride.  Two launches (csrc/memory_scan.cu)."""
+    lib = build.load("memory_scan")
+    n = q.shape[0]
+    if gates.dtype != torch.float32 or not gates.is_contiguous() or gates.numel() < n * heads * 4 or m_state.dtype != torch.float32:
+        raise KernelError("mlstm_gates: gates and the maxima are float32")
+    _check(lib, lib.llmk_mlstm_gates(_ptr(gates), _ptr(q), c_longlong(_row_stride(q)), _ptr(k), c_longlong(_row_stride(k)), _ptr(gi),
+                                     c_longlong(_row_stride(gi)), _ptr(gf), c_longlong(_row_stride(gf)), _ptr(bias_i), _ptr(bias_f),
+                                     _ptr(m_state), c_longlong(_row_stride(m_state)), _ptr(cu_q), _ptr(state_slots), c_int(n_seqs),
+                                     c_int(n), c_int(heads), c_int(dim), c_float(cap), c_float(q_scale), c_int(dtype_code(q.dtype)),
+                                     _stream()), 2)
+
+
+def delta_rule_prep(aux: torch.Tensor, dots: torch.Tensor, r: torch.Tensor, k: torch.Tensor, a: torch.Tensor, decay: torch.Tensor,
+                    a_bias: Optional[torch.Tensor], w_bias: Optional[torch.Tensor], cu_q: torch.Tensor, n_seqs: int, heads: int, dim: int,
+                    decay_scale: float, unit_eps: float) -> None:
+    """The generalized delta rule's vectors per token and head: aux float32 [n, 3 heads dim] = [w | b | u] with w = exp(-decay_scale
+    sigmoid(decay + w_bias)), u = k / sqrt(sum k^2 + unit_eps), b = sigmoid(a + a_bias) u; dots float32 [n, heads, 2] = (b . r, k . r).
+    r, k, a of the storage dtype with any row stride; decay float32."""
+    lib = build.load("memory_scan")
+    n = r.shape[0]
+    if aux.dtype != torch.float32 or dots.dtype != torch.float32 or decay.dtype != torch.float32 or not aux.is_contiguous() \
+            or not dots.is_contiguous() or aux.numel() < n * 3 * heads * dim or dots.numel() < n * heads * 2:
+        raise KernelError("delta_rule_prep: aux, dots and the decay's input are float32")
+    _check(lib, lib.llmk_delta_rule_prep(_ptr(aux), _ptr(dots), _ptr(r), c_longlong(_row_stride(r)), _ptr(k), c_longlong(_row_stride(k)),
+                                         _ptr(a), c_longlong(_row_stride(a)), _ptr(decay), c_longlong(_row_stride(decay)), _ptr(a_bias),
+                                         _ptr(w_bias), _ptr(cu_q), c_int(n_seqs), c_int(n), c_int(heads), c_int(dim),
+                                         c_float(decay_scale), c_float(unit_eps), c_int(dtype_code(r.dtype)), _stream()))
+
+
+MEMORY_FORMS = {"delta": 0, "mlstm": 1}
+
+
+def memory_scan(out: torch.Tensor, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, aux: Optional[torch.Tensor], dots: torch.Tensor,
+                state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int, heads: int, dim: int, vdim: int,
+                form: str, r_scale: float = 1.0, den_eps: float = 0.0) -> None:
+    """A matrix memory S [dim, vdim] per head walked over each sequence's new tokens (csrc/memory_scan.cu); out float32
+    [n, heads vdim].  "delta": S_t = diag(w) S - b (u^T S) + k v^T, o = S_t^T r, with `aux` and `dots` from `delta_rule_prep`.
+    "mlstm": S_t = keep S + take k v^T, n_t = keep n + take k, o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + den_eps), q = r r_scale,
+    with `dots` from `mlstm_gates`.  state float32 [slots, >= heads dim vdim (+ heads dim for n)]."""
+    lib = build.load("memory_scan")
+    need = heads * dim * vdim + (heads * dim if form == "mlstm" else 0)
+    if out.dtype != torch.float32 or not out.is_contiguous() or state.dtype != torch.float32 or state.shape[1] < need \
+            or dots.dtype != torch.float32 or r.dtype != k.dtype or r.dtype != v.dtype:
+        raise KernelError("memory_scan: out, dots and state are float32; r, k, v share the storage dtype")
+    _check(lib, lib.llmk_memory_scan(_ptr(out), _ptr(r), c_longlong(_row_stride(r)), _ptr(k), c_longlong(_row_stride(k)), _ptr(v),
+                                     c_longlong(_row_stride(v)), _ptr(aux), _ptr(dots), _ptr(state), c_longlong(_row_stride(state)),
+                                     _ptr(cu_q), _ptr(state_slots), c_int(n_seqs), c_int(heads), c_int(dim), c_int(vdim),
+                                     c_int(MEMORY_FORMS[form]), c_float(r_scale), c_float(den_eps), c_int(dtype_code(r.dtype)), _stream()))
 
 
 # ------------------------------------------------------------------------------ recurrent mixers

@@ -1,2 +1,2 @@
 """Built-in architectures; importing this package registers them."""
-from . import derupel, fonuvik, qwen3, sarulix  # noqa: F401
+from . import derupel, fonuvik, nasozen, qwen3, sarulix  # noqa: F401

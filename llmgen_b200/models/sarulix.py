@@ -38,9 +38,9 @@ RGLRU_DECAY_SCALE = 8.0
 UNIT_EPS = 1e-6
 
 
-def sarulix_run_order(n_layers: int, loop):
+def sarulix_run_order(n_layers: int, loop, reentry: bool = True):
     """The run list: layers before the loop, the loop's layers `times` times (each appearance with a cache number of
-    its own, the first of a pass behind a `ReentrySpec`), the rest."""
+    its own, the first of a pass behind a `ReentrySpec` unless `reentry` is off), the rest."""
     if loop is None:
         return tuple(RunItem(layer=i, cache=i) for i in range(n_layers))
     items, cache = [], 0
@@ -49,7 +49,7 @@ def sarulix_run_order(n_layers: int, loop):
         cache += 1
     for t in range(loop.times):
         for i in range(loop.start, loop.stop):
-            before = ReentrySpec("loop.in", "loop.step", t, loop.times) if i == loop.start else None
+            before = ReentrySpec("loop.in", "loop.step", t, loop.times) if reentry and i == loop.start else None
             items.append(RunItem(layer=i, cache=cache, before=before))
             cache += 1
     for i in range(loop.stop, n_layers):

@@ -5,10 +5,10 @@ import torch
 
 from ..cache.manager import FULL, WINDOW
 from ..kernels import ops
-from .base import KVRequest, LayerCache, Mixer
+from .base import KVRequest, LayerCache, Mixer, StateRequest
 from .linear import GEMM_MODULES, linear, linear_sliced
 from .registry import build_position, norm_class, register_mixer
-from .spec import INIT_ONE_PLUS_NORMAL, VECTOR, AttentionSpec, WeightDecl
+from .spec import INIT_ONE_PLUS_NORMAL, VECTOR, AttentionSpec, RopeSpec, WeightDecl
 
 
 def add_query_tiles(builder, bq: int, window: int = 0, heaviest_first: bool = False) -> str:
@@ -80,16 +80,20 @@ class GQAAttention(Mixer):
             if name:
                 decls.append(WeightDecl(name, (width,), VECTOR))
         if spec.gate_proj:
-            decls.append(WeightDecl(spec.gate_proj, (od, spec.hidden_size)))
+            decls.append(WeightDecl(spec.gate_proj, (spec.num_heads if spec.gate_per_head else od, spec.hidden_size)))
         for n in (spec.q_norm, spec.k_norm):
             if n is not None:
                 decls += norm_class(n).weight_decls(n)
+        if spec.conv is not None:
+            decls += [WeightDecl(n, (w, spec.conv.taps), VECTOR) for n, w in zip(spec.conv_weights, (qd, kd, vd))]
+        if spec.sink_scores:
+            decls.append(WeightDecl(spec.sink_scores, (spec.num_heads,), VECTOR))
         return decls
 
     @staticmethod
     def kernel_modules(spec):
         if GQAAttention.varied(spec):
-            return ("attn_prep", "attention", "attention_mma", "rowwise") + GEMM_MODULES
+            return ("attn_prep", "attention", "attention_mma", "rowwise") + (("recurrent",) if spec.conv is not None else ()) + GEMM_MODULES
         return ("attn_prep", "attention", "attention_decode", "attention_tc") + GEMM_MODULES
 
     @staticmethod
@@ -97,6 +101,7 @@ class GQAAttention(Mixer):
         """True for a layer that only the general kernels take (see the class's last paragraph)."""
         return bool(spec.q_bias or spec.k_bias or spec.v_bias or spec.o_bias or spec.gate_proj or spec.sink or spec.softcap > 0
                     or spec.value_dim != spec.head_dim or spec.chunk or spec.unit_norm_eps is not None
+                    or spec.conv is not None or spec.row_norms or spec.rotate_values or spec.sink_scores or spec.gate_per_head
                     or (spec.position is not None and getattr(spec.position, "pairing", "half") != "half"))
 
     def __init__(self, spec: AttentionSpec, weights, dtype, device):
@@ -104,8 +109,11 @@ class GQAAttention(Mixer):
             raise ValueError(f"attention: {spec.num_heads} heads are not a multiple of {spec.num_kv_heads} kv heads")
         if spec.head_dim % 2 != 0 or spec.head_dim > 512:
             raise ValueError(f"attention: head_dim {spec.head_dim} must be even, at most 512")
-        for n in (spec.q_norm, spec.k_norm):
-            if n is not None and (n.kind not in ops.HEAD_NORMS or n.dim != spec.head_dim):
+        for n, heads in ((spec.q_norm, spec.num_heads), (spec.k_norm, spec.num_kv_heads)):
+            if n is not None and spec.row_norms:
+                if n.kind != "rmsnorm" or n.dim != heads * spec.head_dim or n.weight_offset != 0.0:
+                    raise ValueError("attention: norms over a whole projection are plain RMSNorms of that width")
+            elif n is not None and (n.kind not in ops.HEAD_NORMS or n.dim != spec.head_dim):
                 raise ValueError(f"attention: per-head norms must run over head_dim and be one of {sorted(ops.HEAD_NORMS)}")
         self.spec = spec
         self.dtype = dtype
@@ -146,6 +154,33 @@ class GQAAttention(Mixer):
             if spec.q_norm or spec.k_norm:
                 raise ValueError("attention: per-head norms before the rotation and a unit norm after it exclude each other")
             self.head_norm, self.norm_eps = "unit_rms_after", float(spec.unit_norm_eps)
+        # the variations that come with norms over whole projections: a short convolution after the projections (its last
+        # inputs are state), values rotated by their position and outputs turned back, learned sink scores, a gate per head
+        self.row_norms = bool(spec.row_norms)
+        self.conv_w = None
+        if spec.conv is not None:
+            C = (self.nq + self.nkv) * self.hd + self.nkv * self.vd
+            if spec.conv.channels != C or not 1 <= spec.conv.taps <= 8 or len(spec.conv_weights) != 3:
+                raise ValueError("attention: one convolution of 1 to 8 taps over the channels of q, k and v")
+            if not spec.row_norms:
+                raise ValueError("attention: the convolution after the projections comes with norms over whole projections")
+            self.conv_w = torch.cat([weights.device_tensor(n, dtype, device, keep=False) for n in spec.conv_weights], dim=0).contiguous()
+        self.value_position = None
+        if spec.rotate_values:
+            if spec.position is None or self.vd % 2 != 0 or not spec.row_norms:
+                raise ValueError("attention: rotated values need a position encoding, an even width and norms over whole projections")
+            if getattr(spec.position, "pairing", "half") != "half" or getattr(spec.position, "scaling", None) is not None:
+                raise ValueError("attention: rotated values are turned in half-split pairs by plain frequencies")
+            self.value_position = build_position(RopeSpec(rotary_dim=self.vd, theta=spec.position.theta,
+                                                          max_positions=spec.position.max_positions), weights, dtype, device)
+        if spec.row_norms and (spec.q_bias or spec.k_bias or spec.v_bias or spec.softcap > 0 or spec.chunk or spec.unit_norm_eps is not None
+                               or self.pairing != "half"):
+            raise ValueError("attention: norms over whole projections exclude biases, a bound, a mask in blocks and other pairings")
+        if (spec.sink_scores or spec.gate_per_head) and not spec.row_norms:
+            raise ValueError("attention: learned sink scores and a gate per head come with norms over whole projections")
+        self.sink_scores = weights.device_tensor(spec.sink_scores, dtype, device).contiguous() if spec.sink_scores else None
+        if self.sink_scores is not None and not spec.sink:
+            raise ValueError("attention: sink scores without a sink")
         self.chunk = int(spec.chunk or 0)
         if self.chunk and spec.window:
             raise ValueError("attention: a window and a mask in blocks exclude each other")
@@ -163,6 +198,12 @@ class GQAAttention(Mixer):
         held = self.window or self.chunk
         return KVRequest(WINDOW if held else FULL, held, self.nkv, self.hd,
                          v_head_dim=self.vd if self.vd != self.hd else 0)
+
+    def state_request(self):
+        # the convolution's last taps - 1 inputs over the channels of q, k and v side by side, oldest first
+        if self.conv_w is None or self.spec.conv.taps <= 1:
+            return None
+        return StateRequest(((self.spec.conv.taps - 1) * self.conv_w.shape[0],), torch.float32)
 
     def max_positions(self):
         return self.position.max_positions if self.position is not None else None
@@ -288,6 +329,8 @@ class GQAAttention(Mixer):
         """A layer with biases, another value width, a bound on the scores, a sink or a gate: the packed projection as
         an array (the gate's columns are read from it as they are), the general preparation and attention kernels."""
         T, ws = ctx.n_tokens, ctx.workspace
+        if self.row_norms:
+            return self._forward_row_norms(ctx, x, cache, group, cos, sin, rot)
         w = self.w_qkv if cache.writes else self.w_q_gate
         packed = linear(x, w, ws.buffer("attn_qkvg" if cache.writes else "attn_qg", T, w.shape[0], self.dtype))
         gate = None
@@ -322,6 +365,61 @@ class GQAAttention(Mixer):
                             ctx.ctx_len, ctx.cu_q, tile_seq, tile_q0, tile_seq.numel(), T, self.nq, self.nkv,
                             self.hd, cache.page_size, self.window, float(self.spec.scale), parts, part_size, scratch,
                             vd=self.vd, softcap=self.softcap, sink=self.sink, gate=gate, chunk=self.chunk)
+        out = linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
+        if self.o_bias is not None:
+            ops.add_bias(out, self.o_bias)
+        return out
+
+    def _forward_row_norms(self, ctx, x, cache, group, cos, sin, rot):
+        """A layer whose q and k are normed over their whole projections: the packed projection [q | k | v | gate], the short
+        convolution over the channels of q, k, v (float32 out; its history from and to the request's state), one kernel for both
+        norms, the rotation of q and k, the rotation of v and the cache write, attention with the heads' sink scores, and one
+        kernel that turns each head's output back and applies the head's gate."""
+        T, ws = ctx.n_tokens, ctx.workspace
+        if not cache.writes:
+            raise ValueError("attention: a layer with norms over whole projections writes its own cache")
+        nq, nk, hd, vd = self.nq, self.nkv, self.hd, self.vd
+        C = (nq + nk) * hd + nk * vd
+        if self.conv_w is not None:
+            packed = linear(x, self.w_qkv, ws.buffer("attn_qkvg", T, self.w_qkv.shape[0], self.dtype))
+            rows = ws.buffer("attn_conv", T, C, torch.float32)
+            state = cache.state if cache.state is not None else ws.buffer("attn_no_state", 1, 1, torch.float32)
+            ops.short_conv(rows, packed[:, :C], self.conv_w, state, ctx.cu_q, ctx.state_slots, ctx.n_seqs,
+                           update_state=cache.state is not None)
+            gate = packed[:, self.gate_off:] if self.gate_off >= 0 else None
+        else:
+            # the norms' kernel reads float32 rows: the projection leaves in float32
+            rows = linear(x, self.w_qkv, ws.buffer("attn_qkvg32", T, self.w_qkv.shape[0], torch.float32))
+            gate = None
+            if self.gate_off >= 0:
+                gate = ws.buffer("attn_gate", T, self.w_qkv.shape[0] - self.gate_off, self.dtype)
+                ops.cast_rows(gate, rows[:, self.gate_off:].contiguous())
+        vcos, vsin = self.value_position.tables() if self.value_position is not None else (None, None)
+        q = ws.buffer("attn_q", T, nq * hd, self.dtype)
+        ops.attn_prep_rows(rows, q, cache.k, cache.v, ctx.positions, group.slots, cos, sin, vcos, vsin, self.q_gain, self.k_gain,
+                           nq, nk, hd, vd, rot, cache.page_size, self.norm_eps)
+        o = ws.buffer("attn_o", T, nq * vd, self.dtype)
+        per_head = self.spec.gate_per_head
+        inside = None if per_head else gate          # a gate per value is applied inside the attention kernels
+        mma_bq = 0 if ctx.pure_decode else self.mma_tile_queries()
+        if mma_bq and ctx.has_array(f"attention_tiles_bq{mma_bq}_seq"):
+            tile_seq = ctx.array(f"attention_tiles_bq{mma_bq}_seq")
+            ops.attention_mma(o, q, cache.k, cache.v, group.block_tables, group.max_blocks, ctx.ctx_len, ctx.cu_q, tile_seq,
+                              ctx.array(f"attention_tiles_bq{mma_bq}_q0"), tile_seq.numel(), nq, nk, hd, vd, cache.page_size, self.window,
+                              float(self.spec.scale), sink=self.sink, gate=inside, sink_values=self.sink_scores)
+        else:
+            tile_seq = ctx.array(self.tiles_name + "_seq")
+            tile_q0 = ctx.array(self.tiles_name + "_q0")
+            parts, part_size = self._split(ctx)
+            scratch = None
+            if parts > 1:
+                scratch = ws.flat("attn_split", ops.attention_scratch_floats(T, nq, vd, parts), torch.float32)
+            ops.paged_attention(o, q, q.stride(0), cache.k, cache.v, group.block_tables, group.max_blocks, ctx.ctx_len, ctx.cu_q,
+                                tile_seq, tile_q0, tile_seq.numel(), T, nq, nk, hd, cache.page_size, self.window,
+                                float(self.spec.scale), parts, part_size, scratch, vd=vd, sink=self.sink, gate=inside,
+                                sink_values=self.sink_scores)
+        if vcos is not None or (per_head and gate is not None):
+            ops.unrotate_gate(o, gate if per_head else None, ctx.positions, vcos, vsin, nq, vd)
         out = linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
         if self.o_bias is not None:
             ops.add_bias(out, self.o_bias)

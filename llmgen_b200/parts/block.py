@@ -8,7 +8,7 @@ from .registry import (build_feed_forward, build_mixer, build_norm, feed_forward
                        register_block)
 from ..kernels import ops
 from .parallel import finish_pair
-from .spec import PostNormBlockSpec, PreNormBlockSpec, SandwichBlockSpec
+from .spec import VECTOR, MultiStreamBlockSpec, PostNormBlockSpec, PreNormBlockSpec, SandwichBlockSpec, WeightDecl
 
 
 class PreNormBlock(Part):
@@ -197,6 +197,100 @@ class SandwichBlock(Part):
         return None
 
 
+class MultiStreamBlock(Part):
+    """A pre-norm layer over several residual streams per token (hyper-connections).
+
+    The block's `resid` is the float32 array [tokens, streams * hidden] that the model keeps for architectures with
+    `residual_streams`.  One kernel (`stream_step`) lies between two sublayers: it rewrites every stream from all the old ones
+    and the sublayer's output (an array, float32 slices, or the weighted pair a parallel mixer returns), x_t <- sum_s mix[s, t] x_s +
+    mult write[t] y, and in the same pass reads the streams for the sublayer that follows, norm(sum_t read[t] x_t) (the next block's
+    mixer included, when the run list's next item is a block of this kind: the model names it in `ctx.next_block`).  The
+    coefficients stay float32; `mult write` is folded at load.  A block whose input nobody prepared reads the streams itself.
+    It finishes its sums and hands on nothing to add."""
+
+    @staticmethod
+    def weight_decls(spec: MultiStreamBlockSpec):
+        S = spec.streams
+
+        def coefficients(c):
+            return [] if c is None else [WeightDecl(c.read, (S,), VECTOR), WeightDecl(c.write, (S,), VECTOR), WeightDecl(c.mix, (S, S), VECTOR)]
+
+        decls = norm_class(spec.mixer_norm).weight_decls(spec.mixer_norm) + mixer_class(spec.mixer).weight_decls(spec.mixer) \
+            + coefficients(spec.mixer_streams)
+        if spec.ffn is not None:
+            decls += norm_class(spec.ffn_norm).weight_decls(spec.ffn_norm) + feed_forward_class(spec.ffn).weight_decls(spec.ffn) \
+                + coefficients(spec.ffn_streams)
+        return decls
+
+    @staticmethod
+    def kernel_modules(spec: MultiStreamBlockSpec):
+        mods = ("rowwise", "elementwise") + tuple(mixer_class(spec.mixer).kernel_modules(spec.mixer))
+        if spec.ffn is not None:
+            mods += tuple(feed_forward_class(spec.ffn).kernel_modules(spec.ffn))
+        return mods
+
+    def __init__(self, spec: MultiStreamBlockSpec, weights, dtype, device):
+        S = spec.streams
+        if not 1 <= S <= ops.MAX_STREAMS:
+            raise ValueError(f"multi-stream block: {S} streams (1 to {ops.MAX_STREAMS})")
+        for norm in (spec.mixer_norm, spec.ffn_norm if spec.ffn is not None else None):
+            if norm is not None and (norm.kind != "rmsnorm" or norm.weight_offset != 0.0):
+                raise ValueError("multi-stream block: its norms are plain RMSNorms")
+        if S > 1 and (spec.mixer_streams is None or (spec.ffn is not None and spec.ffn_streams is None)):
+            raise ValueError("multi-stream block: several streams need coefficients for every sublayer")
+        self.spec, self.dtype, self.S = spec, dtype, S
+        self.mixer_norm = build_norm(spec.mixer_norm, weights, dtype, device)
+        self.mixer = build_mixer(spec.mixer, weights, dtype, device)
+        self.ffn_norm = build_norm(spec.ffn_norm, weights, dtype, device) if spec.ffn is not None else None
+        self.ffn = build_feed_forward(spec.ffn, weights, dtype, device) if spec.ffn is not None else None
+        mult = float(spec.residual_mult)
+
+        def coefficients(c):
+            # (read, mult * write, mix); without tensors: one stream read as it is, kept as it is, y added times mult
+            if c is None:
+                one = torch.ones(1, dtype=torch.float32, device=device)
+                return one, one * mult, one.clone()
+            return (weights.device_tensor(c.read, dtype, device).contiguous(),
+                    (weights.device_tensor(c.write, dtype, device).float() * mult).contiguous(),
+                    weights.device_tensor(c.mix, dtype, device).contiguous())
+
+        self.read1, self.write1, self.mix1 = coefficients(spec.mixer_streams)
+        self.read2, self.write2, self.mix2 = coefficients(spec.ffn_streams) if spec.ffn is not None else (None, None, None)
+
+    def workspace_bytes(self, tokens: int) -> int:
+        elem = 2 if self.dtype == torch.bfloat16 else 4
+        own = tokens * self.spec.mixer_norm.dim * (elem + 4 * self.S)
+        parts = [getattr(p, "workspace_bytes", None) for p in (self.mixer, self.ffn) if p is not None]
+        return own + max([f(tokens) for f in parts if f is not None] or [0])
+
+    def forward(self, ctx, resid: torch.Tensor, delta, cache: LayerCache):
+        T = resid.shape[0]
+        H = self.spec.mixer_norm.dim
+        if delta is not None or resid.shape[1] != self.S * H:
+            raise ValueError("multi-stream block: it runs on the model's array of streams and takes no pending sum")
+        streams = resid.view(T, self.S, H)
+        normed = ctx.workspace.buffer("block_normed", T, H, self.dtype)
+        if getattr(ctx, "normed_for", None) is not self:
+            ops.stream_step(streams, None, None, None, self.read1, self.mixer_norm.weight, self.mixer_norm.eps, normed, self.dtype)
+        ctx.normed_for = None
+        follower = getattr(ctx, "next_block", None)
+        follow = follower if isinstance(follower, MultiStreamBlock) and follower.S == self.S else None
+        mixed = self.mixer.forward(ctx, normed, cache)
+        if self.ffn is not None:
+            ops.stream_step(streams, mixed, self.mix1, self.write1, self.read2, self.ffn_norm.weight, self.ffn_norm.eps, normed, self.dtype)
+            mixed = self.ffn.forward(ctx, normed)
+            mix, write = self.mix2, self.write2
+        else:
+            mix, write = self.mix1, self.write1
+        if follow is not None:
+            ops.stream_step(streams, mixed, mix, write, follow.read1, follow.mixer_norm.weight, follow.mixer_norm.eps, normed, self.dtype)
+        else:
+            ops.stream_step(streams, mixed, mix, write, None, None, 0.0, None, self.dtype)
+        ctx.normed_for = follow
+        return None
+
+
 register_block("prenorm", PreNormBlock)
+register_block("multi_stream", MultiStreamBlock)
 register_block("sandwich", SandwichBlock)
 register_block("postnorm", PostNormBlock)

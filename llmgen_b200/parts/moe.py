@@ -11,7 +11,7 @@ from .spec import VECTOR, ClampedExpertSpec, DenseMLPSpec, GatedExpertSpec, Gate
 
 
 class DenseMLP(FeedForward):
-    """down( act(x Wup^T) ), act = relu(.)^2: two products and one row-wise kernel between them, which also adds up the
+    """down( act(x Wup^T) ), act = relu(.)^2 or the tanh form of gelu: two products and one row-wise kernel between them, which also adds up the
     float32 slices when the first product was cut along K."""
 
     @staticmethod
@@ -24,7 +24,7 @@ class DenseMLP(FeedForward):
         return ("rowwise",) + GEMM_MODULES
 
     def __init__(self, spec: DenseMLPSpec, weights, dtype, device):
-        if spec.activation not in ops.ACTIVATIONS or spec.activation == "clamped_glu":
+        if spec.activation not in ("relu2", "gelu_tanh"):
             raise ValueError(f"dense feed-forward: activation {spec.activation!r} is not supported")
         self.spec, self.dtype = spec, dtype
         self.w_up = weights.device_tensor(spec.up_proj, dtype, device)

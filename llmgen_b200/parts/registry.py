@@ -141,5 +141,5 @@ def _ensure_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from . import (attention, block, decay_attention, gated_delta, latent_attention, linear_attention, mlp,  # noqa: F401
-                       moe, norm, parallel, rglru, rope)
+        from . import (attention, block, decay_attention, gated_delta, gated_memory, latent_attention, linear_attention,  # noqa: F401
+                       mlp, moe, norm, parallel, rglru, rope)

@@ -113,6 +113,20 @@ class AttentionSpec:
     # floor(j / chunk) = floor(i / chunk), blocks counted from the sequence's first position.
     unit_norm_eps: Optional[float] = None
     chunk: Optional[int] = None
+    # `conv`: a short causal convolution over time on every channel of q, k and v, straight after the projections (one
+    # spec over the channels of q, k and v side by side; `conv_weights` names the three tensors of taps, stacked when the
+    # model is loaded); the sequence's last taps - 1 projected rows are state.  `row_norms`: `q_norm` / `k_norm` run over the
+    # whole projection of a token (all heads at once, gains of that size) instead of over each head.  `rotate_values`: the
+    # value of position j is turned by j over all of its width in half-split pairs (frequencies theta^(-2m / value width),
+    # theta the position encoding's) before it is cached, and each head's output at position i is turned back by -i.
+    # `sink_scores`: with `sink`, the name of a tensor [heads] of learned sink scores (the term is exp(score_h)).
+    # `gate_per_head`: `gate_proj` is [heads, hidden], one number per head.
+    conv: Optional["ShortConvSpec"] = None
+    conv_weights: Tuple[str, ...] = ()
+    row_norms: bool = False
+    rotate_values: bool = False
+    sink_scores: Optional[str] = None
+    gate_per_head: bool = False
     kind: str = "attention"
 
     @property
@@ -310,6 +324,84 @@ class TokenShiftDecaySpec:
 
 
 @dataclass(frozen=True)
+class MinGRUSpec:
+    """A gated recurrence per channel whose gates read the current token only.
+
+    z = sigmoid(x Wz^T + bz), u = x Wx^T + bx, both `width` wide; the candidate is u + 1/2 where u >= 0 and sigmoid(u) below;
+    S_t = (1 - z_t) S_(t-1) + z_t candidate_t, float32, zero before the first token; output (S_t * silu(x Wg^T)) Wo^T.
+    State per request: S."""
+    hidden_size: int
+    width: int
+    z_proj: str
+    x_proj: str
+    gate_proj: str
+    o_proj: str
+    z_bias: Optional[str] = None
+    x_bias: Optional[str] = None
+    kind: str = "min_gru"
+
+
+@dataclass(frozen=True)
+class MLSTMSpec:
+    """A matrix memory per head with exponential gates held in range by a running maximum.
+
+    q = x Wq^T key_dim^(-1/2), k = x Wk^T [heads, key_dim], v = x Wv^T [heads, value_dim]; per head the log gates
+    i = cap tanh((x Wi^T + bi) / cap) and f = logsigmoid(cap tanh((x Wf^T + bf) / cap)).  With m_0 = 0, S_0 = 0, n_0 = 0:
+    m_t = max(f + m_(t-1), i);  S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T;  n_t the same with k alone;
+    o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + den_eps).  Each head's o is divided by its root mean square (eps), the heads
+    side by side are multiplied by `out_gain` [heads value_dim] and sigmoid(x Wg^T), and projected by Wo.  State per request:
+    S, n and m, float32."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    gate_cap: float
+    eps: float
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    i_proj: str
+    f_proj: str
+    gate_proj: str
+    o_proj: str
+    out_gain: str
+    i_bias: Optional[str] = None
+    f_bias: Optional[str] = None
+    den_eps: float = 1e-6
+    kind: str = "mlstm"
+
+
+@dataclass(frozen=True)
+class GeneralDeltaSpec:
+    """The delta rule with a decay per head and key channel and a removal rate of its own.
+
+    r, k, v = x W^T [heads, head_dim].  w = exp(-decay_scale sigmoid(tanh(x Ww1^T) Ww2^T + w0)) and a = sigmoid(x Wa^T + a0), both
+    [heads, head_dim]; u = k / sqrt(sum k^2 + unit_eps) per head.  Per head, S [head_dim, head_dim] float32, zero before the first
+    token:  S_t = diag(w) S_(t-1) - (a u)(u^T S_(t-1)) + k v^T;  o = S_t^T r.  Each head's o is divided by its root mean square (eps),
+    the heads side by side are multiplied by `out_gain` [heads head_dim] and sigmoid(x Wg^T), and projected by Wo.  State per
+    request: S."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    eps: float
+    r_proj: str
+    k_proj: str
+    v_proj: str
+    gate_proj: str
+    o_proj: str
+    removal_proj: str                    # Wa [heads head_dim, hidden]
+    removal_bias: str                    # a0 [heads head_dim]
+    decay_down: str                      # Ww1 [rank, hidden]
+    decay_up: str                        # Ww2 [heads head_dim, rank]
+    decay_bias: str                      # w0 [heads head_dim]
+    out_gain: str
+    decay_rank: int = 16
+    decay_scale: float = 0.6065306597126334      # exp(-1/2)
+    unit_eps: float = 1e-6
+    kind: str = "general_delta"
+
+
+@dataclass(frozen=True)
 class ParallelMixerSpec:
     """Several mixers side by side that read the same input: the result is sum_i scales[i] * branches[i](x).  At most
     one branch keeps paged keys and values; the states of the branches that keep one lie side by side in one row."""
@@ -321,7 +413,7 @@ class ParallelMixerSpec:
 # ---------------------------------------------------------------------- feed-forwards
 @dataclass(frozen=True)
 class DenseMLPSpec:
-    """Feed-forward without a gate: down( act(x Wup^T) ), act = relu(.)^2 ("relu2")."""
+    """Feed-forward without a gate: down( act(x Wup^T) ), act = relu(.)^2 ("relu2") or the tanh form of gelu ("gelu_tanh")."""
     hidden_size: int
     intermediate_size: int
     up_proj: str
@@ -427,6 +519,33 @@ class SandwichBlockSpec:
 
 
 @dataclass(frozen=True)
+class StreamCoefficients:
+    """How one sublayer of a `MultiStreamBlockSpec` reads and writes the streams: tensors `read` [streams], `write` [streams] and
+    `mix` [streams, streams] (indexed [from, to])."""
+    read: str
+    write: str
+    mix: str
+
+
+@dataclass(frozen=True)
+class MultiStreamBlockSpec:
+    """A pre-norm layer over `streams` residual streams x_1 .. x_S per token (hyper-connections), all equal to the embedding's
+    output before the first layer and added up after the last.  Sublayer q (the mixer, then the feed-forward) with its
+    coefficients:  u = sum_s read[s] x_s;  y = sublayer(norm(u));  x_t <- sum_s mix[s, t] x_s + residual_mult write[t] y for all t
+    at once, from the old streams.  Without coefficients (`mixer_streams` / `ffn_streams` None; `streams` is then 1) a sublayer
+    is the plain x <- x + residual_mult sublayer(norm(x)).  `ffn` (with its norm and coefficients) may be None."""
+    mixer_norm: object
+    mixer: object
+    ffn_norm: Optional[object] = None
+    ffn: Optional[object] = None
+    streams: int = 1
+    residual_mult: float = 1.0
+    mixer_streams: Optional[StreamCoefficients] = None
+    ffn_streams: Optional[StreamCoefficients] = None
+    kind: str = "multi_stream"
+
+
+@dataclass(frozen=True)
 class ReentrySpec:
     """What happens to the residual stream before a run item: x <- [x | x0] W^T + table[row], with x0 the embedding's
     output of the same token, W [hidden, 2 hidden] (the stream's columns first) and `table` [rows, hidden]."""
@@ -471,6 +590,9 @@ class ModelSpec:
     logit_cap: float = 0.0               # > 0: logits = cap * tanh(logits / cap)
     logit_scale: float = 1.0             # logits are multiplied by this (before the cap)
     embedding_norm: Optional[object] = None   # a norm spec: the embedding's rows pass it before they become the residual
+    # > 0: the layers keep this many residual streams per token (`MultiStreamBlockSpec`): the model hands them a float32
+    # [tokens, streams, hidden] array, every stream the embedding's output, and adds the streams up before the final norm
+    residual_streams: int = 0
     # Tensors that a model folder of this architecture may carry although the model reads none of them
     # (shell patterns), and (name, declared name) pairs of such tensors that must then hold the same values.
     ignorable_tensors: Tuple[str, ...] = ()
