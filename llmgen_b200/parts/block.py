@@ -8,7 +8,7 @@ from .registry import (build_feed_forward, build_mixer, build_norm, feed_forward
                        register_block)
 from ..kernels import ops
 from .parallel import finish_pair
-from .spec import VECTOR, MultiStreamBlockSpec, PostNormBlockSpec, PreNormBlockSpec, SandwichBlockSpec, WeightDecl
+from .spec import INIT_EYE_PLUS_NORMAL, INIT_ONE_PLUS_NORMAL, VECTOR, MultiStreamBlockSpec, PostNormBlockSpec, PreNormBlockSpec, SandwichBlockSpec, WeightDecl
 
 
 class PreNormBlock(Part):
@@ -213,7 +213,9 @@ class MultiStreamBlock(Part):
         S = spec.streams
 
         def coefficients(c):
-            return [] if c is None else [WeightDecl(c.read, (S,), VECTOR), WeightDecl(c.write, (S,), VECTOR), WeightDecl(c.mix, (S, S), VECTOR)]
+            # the random-weights mode draws them around "every stream read, kept and written as it is"
+            return [] if c is None else [WeightDecl(c.read, (S,), VECTOR, INIT_ONE_PLUS_NORMAL), WeightDecl(c.write, (S,), VECTOR, INIT_ONE_PLUS_NORMAL),
+                                         WeightDecl(c.mix, (S, S), VECTOR, INIT_EYE_PLUS_NORMAL)]
 
         decls = norm_class(spec.mixer_norm).weight_decls(spec.mixer_norm) + mixer_class(spec.mixer).weight_decls(spec.mixer) \
             + coefficients(spec.mixer_streams)

@@ -23,6 +23,7 @@ INT_TABLE = "int_table"  # integer tables: int32
 
 INIT_NORMAL = "normal"              # N(0, sigma)
 INIT_ONE_PLUS_NORMAL = "one_plus"   # 1 + N(0, sigma_norm)
+INIT_EYE_PLUS_NORMAL = "eye_plus"   # a square matrix: the identity + N(0, sigma_norm)
 
 
 @dataclass(frozen=True)

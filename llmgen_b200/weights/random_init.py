@@ -2,7 +2,7 @@
 
 The reference has no such mode; it exists here so that tests and benchmarks need no
 checkpoint.  Matrices and embedding tables are N(0, sigma); norm gains (the per-head q/k
-norms too) are 1 + N(0, sigma_norm).  Each tensor has a generator of its own, seeded from
+norms too) are 1 + N(0, sigma_norm), matrices that mix residual streams the identity + N(0, sigma_norm).  Each tensor has a generator of its own, seeded from
 the run's seed and the tensor's name, so a tensor's values do not depend on which other
 tensors exist or on the order of drawing.
 """
@@ -15,7 +15,7 @@ from typing import Dict, Iterable
 
 import torch
 
-from ..parts.spec import INIT_ONE_PLUS_NORMAL, INT_TABLE, WeightDecl
+from ..parts.spec import INIT_EYE_PLUS_NORMAL, INIT_ONE_PLUS_NORMAL, INT_TABLE, WeightDecl
 from .loader import check_declarations
 from .safetensors_io import write_safetensors
 
@@ -40,6 +40,8 @@ def random_tensors(decls: Iterable[WeightDecl], seed: int, sigma: float, sigma_n
         t = torch.empty(tuple(d.shape), dtype=torch.float32, device=device)
         if d.init == INIT_ONE_PLUS_NORMAL:
             t.normal_(0.0, sigma_norm, generator=g).add_(1.0)
+        elif d.init == INIT_EYE_PLUS_NORMAL:
+            t.normal_(0.0, sigma_norm, generator=g).add_(torch.eye(t.shape[0], t.shape[1], device=device))
         else:
             t.normal_(0.0, sigma, generator=g)
         out[name] = t.to(dtype)

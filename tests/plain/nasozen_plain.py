@@ -97,12 +97,17 @@ def min_gru(h, p):
     u = h @ p["x"].T + p["x.b"]
     cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
     gate = silu(h @ p["g"].T)
-    S = torch.zeros(z.shape[1], dtype=h.dtype)
+    return (min_gru_scan(z, cand)[0] * gate) @ p["o"].T
+
+
+def min_gru_scan(z, cand, S=None):
+    """S_t = (1 - z_t) S_(t-1) + z_t cand_t from S (zeros): every S_t, and the last one."""
+    S = torch.zeros(z.shape[1], dtype=z.dtype) if S is None else S
     rows = []
-    for t in range(T):
+    for t in range(z.shape[0]):
         S = (1.0 - z[t]) * S + z[t] * cand[t]
-        rows.append(S * gate[t])
-    return torch.stack(rows) @ p["o"].T
+        rows.append(S)
+    return torch.stack(rows), S
 
 
 def parallel_mixer(h, p, m, eps):
@@ -126,10 +131,15 @@ def mlstm(h, p, m, eps):
     v = (h @ p["v"].T).view(T, H, E)
     gi = cap * torch.tanh((h @ p["i"].T + p["i.b"]) / cap)
     gf = torch.nn.functional.logsigmoid(cap * torch.tanh((h @ p["f"].T + p["f.b"]) / cap))
-    S = torch.zeros(H, D, E, dtype=h.dtype)
-    n = torch.zeros(H, D, dtype=h.dtype)
-    mx = torch.zeros(H, dtype=h.dtype)
-    o = torch.zeros(T, H, E, dtype=h.dtype)
+    return heads_out(mlstm_memory(q, k, v, gi, gf)[0], h, p, eps)
+
+
+def mlstm_memory(q, k, v, gi, gf, state=None):
+    """q, k [T, H, D], v [T, H, E], log gates [T, H]; state (S, n, m) or None for zeros: every o_t and the last state."""
+    T, H, D = q.shape
+    E = v.shape[2]
+    S, n, mx = state if state is not None else (torch.zeros(H, D, E, dtype=q.dtype), torch.zeros(H, D, dtype=q.dtype), torch.zeros(H, dtype=q.dtype))
+    o = torch.zeros(T, H, E, dtype=q.dtype)
     for t in range(T):
         new = torch.maximum(gf[t] + mx, gi[t])
         keep, take = torch.exp(gf[t] + mx - new), torch.exp(gi[t] - new)
@@ -138,7 +148,7 @@ def mlstm(h, p, m, eps):
         mx = new
         den = torch.maximum((n * q[t]).sum(dim=-1).abs(), torch.exp(-mx)) + 1e-6
         o[t] = torch.einsum("hde,hd->he", S, q[t]) / den[:, None]
-    return heads_out(o, h, p, eps)
+    return o, (S, n, mx)
 
 
 def general_delta(h, p, m, eps):
@@ -150,13 +160,19 @@ def general_delta(h, p, m, eps):
     w = torch.exp(-math.exp(-0.5) * torch.sigmoid(torch.tanh(h @ p["w1"].T) @ p["w2"].T + p["w0"])).view(T, H, D)
     a = torch.sigmoid(h @ p["a"].T + p["a.b"]).view(T, H, D)
     u = k / torch.sqrt((k * k).sum(dim=-1, keepdim=True) + 1e-6)
-    S = torch.zeros(H, D, D, dtype=h.dtype)
-    o = torch.zeros(T, H, D, dtype=h.dtype)
+    return heads_out(delta_memory(r, k, v, w, a, u)[0], h, p, eps)
+
+
+def delta_memory(r, k, v, w, a, u, S=None):
+    """All [T, H, D]; S [H, D, D] or None for zeros: S_t = diag(w) S - (a u)(u^T S) + k v^T, o_t = S_t^T r; every o_t and the last S."""
+    T, H, D = r.shape
+    S = torch.zeros(H, D, v.shape[2], dtype=r.dtype) if S is None else S
+    o = torch.zeros(T, H, v.shape[2], dtype=r.dtype)
     for t in range(T):
         seen = torch.einsum("hd,hde->he", u[t], S)
         S = w[t][:, :, None] * S - (a[t] * u[t])[:, :, None] * seen[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
         o[t] = torch.einsum("hde,hd->he", S, r[t])
-    return heads_out(o, h, p, eps)
+    return o, S
 
 
 # --------------------------------------------------------------------------------------------- feed-forwards
