@@ -1,10 +1,13 @@
-"""`bench.py --designs`: Derupel (or, with `--designs-family sarulix` or `fonuvik`, that design) beside Qwen3 at equal
-layer sizes, random weights, one B200.
+"""`bench.py --designs`: Derupel (or, with `--designs-family sarulix`, `fonuvik` or `nasozen`, that design) beside Qwen3 at equal
+layer sizes, random weights, one B200; `--designs-beside` names another design to stand beside it (Nasozen stands beside
+Fonuvik, the closest model, unless told otherwise).
 
 For each size two models are built: a Derupel whose layers alternate its two mixers and its two feed-forwards (a Sarulix
 whose four layers are a recurrent unit, the delta rule, attention and a recurrent unit again, each with a feed-forward,
 entered once through its loop's mixing step; a Fonuvik whose layers alternate the parallel mixer and the token-shift
-mixer, each with a routed feed-forward whose chosen and shared experts together are as wide as the dense one), and the
+mixer, each with a routed feed-forward whose chosen and shared experts together are as wide as the dense one; a Nasozen of
+four residual streams whose layers are the parallel mixer, the generalized delta rule, the parallel mixer and the matrix
+memory under a running maximum, three with a routed feed-forward and one with a dense one), and the
 Qwen3 of the same width, depth, feed-forward width and vocabulary.
 Measured for both:
 
@@ -74,7 +77,23 @@ def fonuvik_config(s: dict) -> dict:
     return {"architecture": "Fonuvik", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6}, "layers": layers, "max_positions": CONTEXT}
 
 
-FAMILIES = {"derupel": derupel_config, "sarulix": sarulix_config, "fonuvik": fonuvik_config}
+def nasozen_config(s: dict) -> dict:
+    W, heads, hd = s["width"], s["heads"], s["hd"]
+    routed = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"]}, "expert": {"ff": s["expert_ff"]}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    left = {"heads": heads, "kv_heads": max(1, heads // 2), "dim": hd, "vdim": hd, "scale": hd ** -0.5, "conv": 4, "mask": {"size": 1024},
+            "rot": {"base": 500000.0, "dims": hd // 2}}
+    par = {"type": "parallel", "mixer": {"left": left, "right": {"width": W}, "left_scale": 1.0, "right_scale": 0.5}, "mlp": routed}
+    rule = {"type": "general_delta", "mixer": {"heads": W // 64, "dim": 64, "decay_rank": 64}, "mlp": routed}
+    memory = {"type": "mlstm", "mixer": {"heads": max(1, heads // 2), "dim": hd, "vdim": hd, "gate_cap": 15.0}, "mlp": dense}
+    layers = ([par, rule, par, memory] * s["layers"])[: s["layers"]]
+    return {"architecture": "Nasozen", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6}, "residual_mult": 0.7, "streams": 4,
+            "layers": layers, "max_positions": CONTEXT}
+
+
+FAMILIES = {"derupel": derupel_config, "sarulix": sarulix_config, "fonuvik": fonuvik_config, "nasozen": nasozen_config}
+# the design that stands beside a family's where it is not Qwen3: the framework's closest model
+BESIDE = {"nasozen": "fonuvik"}
 
 
 def qwen3_config(s: dict) -> dict:
@@ -195,7 +214,9 @@ def run(args, root: str, sampler=None) -> dict:
     for name in wanted:
         entry = {}
         family = getattr(args, "designs_family", "") or "derupel"
-        for design, cfg in ((family, FAMILIES[family](SIZES[name])), ("qwen3", qwen3_config(SIZES[name]))):
+        beside = getattr(args, "designs_beside", "") or BESIDE.get(family, "qwen3")
+        other = qwen3_config(SIZES[name]) if beside == "qwen3" else FAMILIES[beside](SIZES[name])
+        for design, cfg in ((family, FAMILIES[family](SIZES[name])), (beside, other)):
             model = random_model(cfg, 2, "bfloat16", init_on_device=True)
             res = _throughput(torch, model, args.batch, steps, warmup, 3)
             res["weights_gb"] = round(model.weight_bytes() / 1e9, 3)

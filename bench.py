@@ -4,8 +4,8 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
                     [--shape 0.6b|8b|32b --layers L]      (other layer sizes, beside the default run)
     python bench.py --kernels [--kernels-out FILE.md]     (kernel by kernel beside the reference's own kernels)
-    python bench.py --designs [--designs-family derupel|sarulix|fonuvik] [--designs-out FILE.md]
-                                                          (that design beside Qwen3 at equal layer sizes)
+    python bench.py --designs [--designs-family derupel|sarulix|fonuvik|nasozen] [--designs-beside DESIGN] [--designs-out FILE.md]
+                                                          (that design beside Qwen3, or beside the named design, at equal layer sizes)
 
 Prints ONE JSON line.  A "step" is one decode step of `--batch` sequences (default 8) whose
 prompts are 512 uniform-random token ids; weights are random (seed 2), bfloat16.
@@ -217,8 +217,10 @@ def main():
                     help="Derupel beside Qwen3 at equal layer sizes: prefill and decode throughput and every kernel's share of the "
                          "measured peaks (baseline/design_compare.py); prints one JSON line of its own")
     ap.add_argument("--designs-size", default="", help="with --designs: only these sizes (comma-separated; default all)")
-    ap.add_argument("--designs-family", default="derupel", choices=["derupel", "sarulix", "fonuvik"],
+    ap.add_argument("--designs-family", default="derupel", choices=["derupel", "sarulix", "fonuvik", "nasozen"],
                     help="with --designs: the architecture measured beside Qwen3 (default derupel)")
+    ap.add_argument("--designs-beside", default="", choices=["", "qwen3", "derupel", "sarulix", "fonuvik", "nasozen"],
+                    help="with --designs: the design that stands beside it (default: Qwen3; for nasozen, fonuvik, the closest model)")
     ap.add_argument("--designs-out", default="", help="with --designs: also write the tables as markdown to this file")
     args = ap.parse_args()
 

@@ -5,8 +5,8 @@
 //                   below; out = S_t * silu(g_t)
 //   mlstm_gates     the log gates of a matrix memory with a running maximum, i = cap tanh(. / cap) and
 //                   f = logsigmoid(cap tanh(. / cap)) per token and head, with the token's own q . k
-//   mlstm_maxima    m_t = max(f_t + m_(t-1), i_t) along each sequence (m carried in the state, 0 for a fresh request) and
-//                   from it what the memory's step needs: exp(f + m_(t-1) - m_t), exp(i - m_t), exp(-m_t)
+//   mlstm_maxima    m_t = max(f_t + m_(t-1), i_t) along each sequence (m carried in the state, 0 for a fresh request); what
+//                   the memory's step needs follows from it where it is used: exp(f + m_(t-1) - m_t), exp(i - m_t), exp(-m_t)
 //   delta_rule_prep the generalized delta rule's vectors per token and head: the decay w = exp(-c0 sigmoid(z + w0)), the unit
 //                   key u = k / sqrt(sum k^2 + unit_eps), the removal b = sigmoid(a + a0) u, and the dots b . r and k . r
 //   memory_scan     the memory S [key_dim, value_dim] per head over each sequence's new tokens, in two forms:
@@ -93,7 +93,9 @@ __global__ void mlstm_gates_kernel(float* __restrict__ gates, const T* __restric
     }
 }
 
-// A thread per (sequence, head) walks the tokens: gates[t, h] <- (keep, take, exp(-m_t), take (q . k)).
+// A thread per (sequence, head) walks the tokens with nothing but an add and a maximum in its chain:
+// gates[t, h].w <- m_(t-1), the maximum before the token.  What the memory's step needs follows from (i, f, m_(t-1)) alone,
+// m_t = max(f + m_(t-1), i), keep = exp(f + m_(t-1) - m_t), take = exp(i - m_t), exp(-m_t), and is made where it is used.
 __global__ void mlstm_maxima_kernel(float* __restrict__ gates, float* __restrict__ m_state, long long state_ld,
                                     const int* __restrict__ cu_q, const int* __restrict__ state_slots, int n_seqs, int H) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -106,13 +108,12 @@ __global__ void mlstm_maxima_kernel(float* __restrict__ gates, float* __restrict
     const int slot = state_slots[s];
     float m = slot >= 0 ? m_state[(size_t)slot * state_ld + h] : 0.f;
     float4* g = reinterpret_cast<float4*>(gates);
+#pragma unroll 8
     for (int j = 0; j < n; ++j) {
-        float4 v = g[(size_t)(q_beg + j) * H + h];
-        const float mn = fmaxf(v.y + m, v.x);
-        const float keep = expf(v.y + m - mn), take = expf(v.x - mn);
-        m = mn;
-        v.x = keep; v.y = take; v.w = take * v.z; v.z = expf(-mn);
-        g[(size_t)(q_beg + j) * H + h] = v;
+        float4* at = g + (size_t)(q_beg + j) * H + h;
+        const float2 gate = *reinterpret_cast<const float2*>(at);
+        at->w = m;
+        m = fmaxf(gate.y + m, gate.x);
     }
     if (slot >= 0) m_state[(size_t)slot * state_ld + h] = m;
 }
@@ -177,7 +178,7 @@ struct ScanParams {
     const void *r, *k, *v;    // storage type, rows ldr / ldk / ldv apart
     long long ldr, ldk, ldv;
     const float* aux;         // delta: [n, 3 H D] = w | b | u
-    const float* dots;        // delta: [n, H, 2] = (b . r, k . r); mlstm: [n, H, 4] = (keep, take, exp(-m), take (q . k) q_scale)
+    const float* dots;        // delta: [n, H, 2] = (b . r, k . r); mlstm: [n, H, 4] = (i, f, (q . k) q_scale, m before the token)
     float* state;             // [slots, state_ld]: S [H, D, E], then (mlstm) n [H, D]
     long long state_ld;
     const int *cu_q, *state_slots;
@@ -231,8 +232,15 @@ __global__ void __launch_bounds__(LANES* CT) memory_scan_kernel(ScanParams p) {
                 val = ee < E ? to_float(vp[t * p.ldv + (size_t)h * E + ee]) : 0.f;
             } else {
                 const int q = o - vecs * D - CT;
-                if (FORM == FORM_DELTA) val = q < 2 ? p.dots[(t * H + h) * 2 + q] : 0.f;
-                else val = p.dots[(t * H + h) * 4 + q];
+                if (FORM == FORM_DELTA) {
+                    val = q < 2 ? p.dots[(t * H + h) * 2 + q] : 0.f;
+                } else {
+                    // (i, f, (q . k) q_scale, m before the token) -> keep, take, exp(-m_t), take (q . k) q_scale
+                    const float4 g = reinterpret_cast<const float4*>(p.dots)[t * H + h];
+                    const float mn = fmaxf(g.y + g.w, g.x);
+                    const float take = expf(g.x - mn);
+                    val = q == 0 ? expf(g.y + g.w - mn) : q == 1 ? take : q == 2 ? expf(-mn) : take * g.z;
+                }
             }
             sm[i] = val;
         }
@@ -357,7 +365,7 @@ LLMK_EXPORT int llmk_min_gru(void* out, const float* zxg, long long ld, const fl
     return LLMK_OK;
 }
 
-// gates [n, H, 4] float32 <- (keep, take, exp(-m), take (q . k) q_scale) per token and head; m [slots, >= H] carried in the state.
+// gates [n, H, 4] float32 <- (i, f, (q . k) q_scale, m before the token) per token and head; m [slots, >= H] carried in the state.
 LLMK_EXPORT int llmk_mlstm_gates(float* gates, const void* q, long long ldq, const void* k, long long ldk, const void* gi, long long ldi,
                                  const void* gf, long long ldf, const float* bi, const float* bf, float* m_state, long long state_ld,
                                  const int* cu_q, const int* state_slots, int n_seqs, int n_rows, int H, int D, float cap, float q_scale,

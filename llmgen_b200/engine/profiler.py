@@ -385,6 +385,52 @@ def _cost_token_shift(a, info: PassInfo) -> Tuple[int, int]:
     return 3 * a["out"].numel(), _nbytes(a["out"]) + 2 * _nbytes(a["x"]) + _nbytes(a["mu"])
 
 
+def _cost_in_place(a, info: PassInfo) -> Tuple[int, int]:
+    """A kernel that rewrites its first operand (`streams`, `o`) from the others."""
+    first = a.get("streams", a.get("o"))
+    return (first.numel() if hasattr(first, "numel") else 0), sum(_nbytes(v) for v in a.values()) + _nbytes(first)
+
+
+def _cost_stream_step(a, info: PassInfo) -> Tuple[int, int]:
+    n, S, H = a["streams"].shape
+    wrote = a.get("y") is not None
+    flops = n * H * ((2 * S * S + 2 * S if wrote else 0) + (2 * S + 5 if a.get("next_in") is not None else 0))
+    return flops, _nbytes(a["streams"]) * (2 if wrote else 1) + _nbytes(a.get("y")) + _nbytes(a.get("normed"))
+
+
+def _cost_attn_prep_rows(a, info: PassInfo) -> Tuple[int, int]:
+    n = a["x"].shape[0]
+    nq, nk, hd, vd = int(a["nq"]), int(a["nk"]), int(a["hd"]), int(a["vd"])
+    cols = nq * hd + nk * (hd + vd)
+    return n * cols * 8, n * cols * (4 + a["q_out"].element_size()) + 2 * n * (int(a["rot"]) + vd) * 4
+
+
+def _cost_memory_scan(a, info: PassInfo) -> Tuple[int, int]:
+    H, D, E = int(a["heads"]), int(a["dim"]), int(a["vdim"])
+    n = a["out"].shape[0]
+    # two dot products over the state and its update, a token (one of the dot products over n alone in the other form)
+    flops = n * H * ((8 if a["form"] == "delta" else 6) * D * E + 8 * D)
+    elem = a["r"].element_size()
+    bytes_ = n * H * (2 * D + E) * elem + _nbytes(a.get("aux")) + _nbytes(a["dots"]) + _nbytes(a["out"]) + 2 * len(info.q_lens) * H * D * E * 4
+    return flops, bytes_
+
+
+def _cost_min_gru(a, info: PassInfo) -> Tuple[int, int]:
+    return 12 * a["out"].numel(), _nbytes(a["zxg"]) + _nbytes(a["out"]) + 2 * len(info.q_lens) * a["out"].shape[1] * 4
+
+
+def _cost_delta_rule_prep(a, info: PassInfo) -> Tuple[int, int]:
+    n = a["r"].shape[0]
+    hd = int(a["heads"]) * int(a["dim"])
+    return 16 * n * hd, n * hd * (3 * a["r"].element_size() + 4) + _nbytes(a["aux"]) + _nbytes(a["dots"])
+
+
+def _cost_mlstm_gates(a, info: PassInfo) -> Tuple[int, int]:
+    n = a["q"].shape[0]
+    hd = int(a["heads"]) * int(a["dim"])
+    return 2 * n * hd, 2 * n * hd * a["q"].element_size() + 3 * _nbytes(a["gates"])
+
+
 def _cost_scaled_sum(a, info: PassInfo) -> Tuple[int, int]:
     return 3 * a["out"].numel(), _nbytes(a["out"]) + _nbytes(a["pair"])
 
@@ -456,6 +502,9 @@ OP_COSTS: Dict[str, Callable] = {
     "short_conv": _cost_short_conv, "rglru": _cost_rglru, "delta_scan": _cost_delta_scan, "add_bias": _cost_all_operands,
     "concat_stream": _cost_all_operands, "logit_cap": _cost_all_operands,
     "decay_scan": _cost_decay_scan, "token_shift_mix": _cost_token_shift, "scaled_sum": _cost_scaled_sum,
+    "stream_step": _cost_stream_step, "stream_spread": _cost_in_place, "attn_prep_rows": _cost_attn_prep_rows,
+    "unrotate_gate": _cost_in_place, "min_gru": _cost_min_gru, "mlstm_gates": _cost_mlstm_gates,
+    "delta_rule_prep": _cost_delta_rule_prep, "memory_scan": _cost_memory_scan,
 }
 
 

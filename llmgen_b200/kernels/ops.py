@@ -964,9 +964,10 @@ def min_gru(out: torch.Tensor, zxg: torch.Tensor, bias_z: Optional[torch.Tensor]
 def mlstm_gates(gates: torch.Tensor, q: torch.Tensor, k: torch.Tensor, gi: torch.Tensor, gf: torch.Tensor, bias_i: Optional[torch.Tensor],
                 bias_f: Optional[torch.Tensor], m_state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_seqs: int,
                 heads: int, dim: int, cap: float, q_scale: float) -> None:
-    """gates float32 [n, heads, 4] <- (keep, take, exp(-m_t), take (q . k) q_scale) of a matrix memory with a running maximum:
-    i = cap tanh((gi + bias_i) / cap), f = logsigmoid(cap tanh((gf + bias_f) / cap)), m_t = max(f + m_(t-1), i), keep = exp(f +
-    m_(t-1) - m_t), take = exp(i - m_t); m is carried in `m_state` (float32 [slots, >= heads]).  q, k [n, heads dim] and gi, gf
+    """gates float32 [n, heads, 4] <- (i, f, (q . k) q_scale, m_(t-1)) of a matrix memory with a running maximum:
+    i = cap tanh((gi + bias_i) / cap), f = logsigmoid(cap tanh((gf + bias_f) / cap)), m_t = max(f + m_(t-1), i) (from which
+    `memory_scan` makes keep = exp(f + m_(t-1) - m_t), take = exp(i - m_t) and exp(-m_t)); m is carried in `m_state` (float32
+    [slots, >= heads]).  q, k [n, heads dim] and gi, gf
     [n, heads] of the storage dtype with any row stride.  Two launches (csrc/memory_scan.cu)."""
     lib = build.load("memory_scan")
     n = q.shape[0]

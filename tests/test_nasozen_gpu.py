@@ -269,7 +269,7 @@ def test_a_state_that_forgets_little_is_carried_through_portions_and_long_decodi
         assert nu.relative_error(restarted[:1], want[cut:cut + 1]) > 100 * nu.TOL["float32"], cut
     # and the first token still counts at the end: without it the last logits differ
     shifted = nu.plain_logits(cfg, tensors, ids[1:])
-    assert nu.relative_error(shifted[-1:], want[-1:]) > 30 * nu.TOL["float32"]
+    assert nu.relative_error(shifted[-1:], want[-1:]) > 5 * nu.TOL["float32"]
 
 
 @pytest.mark.parametrize("name", ["MIXED", "ODD", "PLAIN"])

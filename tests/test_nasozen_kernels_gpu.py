@@ -192,7 +192,9 @@ def test_the_gated_recurrence_carries_its_state_from_step_to_step(C, dtype):
 def test_the_memory_under_a_running_maximum_step_by_step(H, D, E, dtype):
     from llmgen_b200.kernels import ops
     dt, cap = DT[dtype], 6.0
-    tol = 2e-5 if dtype == "float32" else 1e-4           # inputs are the same rounded values on both sides
+    # inputs are the same rounded values on both sides.  The largest outputs are those whose denominator |n . q| is what a
+    # cancellation left, which float32 holds to fewer digits than the sums it came from
+    tol = 1e-4
     bi, bf = rnd((H,), 1), rnd((H,), 2) + 2.0
     size = H * D * E + H * D + H
     state = torch.zeros(5, size + 1, device=DEV)

@@ -287,7 +287,12 @@ def test_every_listed_binding_exists_with_the_operands_its_cost_reads():
              pf._cost_latent_prep: [("packed",), ("q_rank",), ("rank",), ("rot",)], pf._cost_latent_rotate: [("qa",), ("heads",), ("rot",)], pf._cost_moe_route: [("h",), ("router",)],
              pf._cost_moe_experts: [("w0",), ("n_slots",), ("first",)], pf._cost_grouped_product: [("w",), ("a",), ("out",), ("real_rows",)],
              pf._cost_decay_scan: [("heads",), ("dim",), ("vdim",), ("q",), ("k",), ("v",), ("decay",), ("out",)],
-             pf._cost_token_shift: [("out",), ("x",), ("mu",)], pf._cost_scaled_sum: [("out",), ("pair",)]}
+             pf._cost_token_shift: [("out",), ("x",), ("mu",)], pf._cost_scaled_sum: [("out",), ("pair",)],
+             pf._cost_in_place: [("streams", "o")], pf._cost_stream_step: [("streams",), ("y",), ("next_in",), ("normed",)],
+             pf._cost_attn_prep_rows: [("x",), ("q_out",), ("nq",), ("nk",), ("hd",), ("vd",), ("rot",)],
+             pf._cost_memory_scan: [("heads",), ("dim",), ("vdim",), ("form",), ("r",), ("aux",), ("dots",), ("out",)],
+             pf._cost_min_gru: [("out",), ("zxg",)], pf._cost_delta_rule_prep: [("r",), ("heads",), ("dim",), ("aux",), ("dots",)],
+             pf._cost_mlstm_gates: [("q",), ("heads",), ("dim",), ("gates",)]}
     for name, cost in pf.OP_COSTS.items():
         params = inspect.signature(getattr(ops, name)).parameters
         for alternatives in needs[cost]:
