@@ -88,8 +88,9 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
         // part_size <= 0: split this sequence's own keys evenly (whole key tiles per part), so the
         // launch shape does not depend on the context lengths.
         int part_size = p.part_size;
-        if (part_size <= 0) part_size = ceil_div(ceil_div(max(p.chunk > 0 ? k_end - k_beg : ctx, 1), p.num_parts), KT) * KT;
-        const int base = p.chunk > 0 ? k_beg : 0;      // blocks of positions: the parts cut what the tile can see
+        const bool seen_only = p.chunk > 0 || p.window > 0;
+        if (part_size <= 0) part_size = ceil_div(ceil_div(max(seen_only ? k_end - k_beg : ctx, 1), p.num_parts), KT) * KT;
+        const int base = seen_only ? k_beg : 0;        // blocks of positions, a window: the parts cut what the tile can see
         k_beg = max(k_beg, base + part * part_size);
         k_end = min(k_end, base + (part + 1) * part_size);
     }

@@ -2,7 +2,7 @@
 // steps:
 //
 //   min_gru         S_t = (1 - z_t) S_(t-1) + z_t c_t per channel, z = sigmoid(.), c = u + 1/2 where u >= 0 and sigmoid(u)
-//                   below; out = S_t * silu(g_t)
+//                   below; out = S_t * silu(g_t); token by token for steps of a few rows, tiles of 32 tokens scanned by a warp else
 //   mlstm_gates     the log gates of a matrix memory with a running maximum, i = cap tanh(. / cap) and
 //                   f = logsigmoid(cap tanh(. / cap)) per token and head, with the token's own q . k
 //   mlstm_maxima    m_t = max(f_t + m_(t-1), i_t) along each sequence (m carried in the state, 0 for a fresh request); what
@@ -62,6 +62,63 @@ __global__ void min_gru_kernel(T* __restrict__ out, const float* __restrict__ zx
     if (slot >= 0) state[(size_t)slot * state_ld + c] = S;
 }
 
+// The same recurrence for steps of many tokens: a block takes 32 channels of one sequence and walks its tokens 32 at a time.
+// Warp w first makes (1 - z, z cand, silu(g)) of the tile's token w for the 32 channels (rows read whole), then scans channel
+// w over the tile's tokens: steps S -> a S + b compose as (a1, b1) then (a2, b2) = (a1 a2, b1 a2 + b2), five rounds over the
+// lanes; then token w's row goes out.  The sums of a token are regrouped, not changed, against the walk above.
+constexpr int GT = 32;
+template <typename T>
+__global__ void __launch_bounds__(GT* GT) min_gru_tile_kernel(T* __restrict__ out, const float* __restrict__ zxg, long long ld,
+                                                              const float* __restrict__ bz, const float* __restrict__ bx,
+                                                              float* __restrict__ state, long long state_ld,
+                                                              const int* __restrict__ cu_q, const int* __restrict__ state_slots, int C) {
+    __shared__ float sa[GT][GT + 1], sb[GT][GT + 1];
+    const int s = blockIdx.y, cb = blockIdx.x * GT;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int q_beg = cu_q[s], n = cu_q[s + 1] - q_beg;
+    if (n <= 0) return;
+    const int slot = state_slots[s];
+    const int c_row = cb + lane, c_scan = cb + w;                 // this thread's channel as a reader of rows, and as a scanner
+    const float b_z = (bz && c_row < C) ? bz[c_row] : 0.f, b_x = (bx && c_row < C) ? bx[c_row] : 0.f;
+    float carry = (slot >= 0 && c_scan < C) ? state[(size_t)slot * state_ld + c_scan] : 0.f;
+    for (int t0 = 0; t0 < n; t0 += GT) {
+        const int nt = min(GT, n - t0);
+        float gs = 0.f, a = 1.f, b = 0.f;
+        if (w < nt && c_row < C) {
+            const float* row = zxg + (size_t)(q_beg + t0 + w) * ld;
+            const float z = sigmoidf_(row[c_row] + b_z);
+            const float u = row[C + c_row] + b_x;
+            const float g = row[2 * C + c_row];
+            a = 1.f - z;
+            b = z * (u >= 0.f ? u + 0.5f : sigmoidf_(u));
+            gs = g * sigmoidf_(g);
+        }
+        sa[w][lane] = a;
+        sb[w][lane] = b;
+        __syncthreads();
+        a = sa[lane][w];          // token `lane` of channel `w`
+        b = sb[lane][w];
+#pragma unroll
+        for (int o = 1; o < GT; o <<= 1) {
+            const float pa = __shfl_up_sync(0xffffffffu, a, o), pb = __shfl_up_sync(0xffffffffu, b, o);
+            if (lane >= o) {
+                b = fmaf(pb, a, b);
+                a *= pa;
+            }
+        }
+        const float S = fmaf(a, carry, b);
+        carry = __shfl_sync(0xffffffffu, S, nt - 1);
+        __syncthreads();
+        sa[lane][w] = S;
+        __syncthreads();
+        if (w < nt && c_row < C) out[(size_t)(q_beg + t0 + w) * C + c_row] = from_float<T>(sa[w][lane] * gs);
+        __syncthreads();
+    }
+    if (slot >= 0 && c_scan < C && lane == 0) state[(size_t)slot * state_ld + c_scan] = carry;
+}
+
 // ------------------------------------------------------------------------------------------------------- mlstm gates
 // A warp per (token, head): gates[t, h] = (i, f, (q . k) q_scale, -).
 template <typename T>
@@ -93,12 +150,14 @@ __global__ void mlstm_gates_kernel(float* __restrict__ gates, const T* __restric
     }
 }
 
-// A thread per (sequence, head) walks the tokens with nothing but an add and a maximum in its chain:
-// gates[t, h].w <- m_(t-1), the maximum before the token.  What the memory's step needs follows from (i, f, m_(t-1)) alone,
-// m_t = max(f + m_(t-1), i), keep = exp(f + m_(t-1) - m_t), take = exp(i - m_t), exp(-m_t), and is made where it is used.
+// A warp per (sequence, head) takes the tokens 32 at a time: gates[t, h].w <- m_(t-1), the maximum before the token.  A token's
+// step m -> max(f + m, i) composes with the next, (f1, i1) then (f2, i2) = (f1 + f2, max(i1 + f2, i2)), so five rounds over the
+// lanes give every token's maximum.  What the memory's step needs follows from (i, f, m_(t-1)) alone, m_t = max(f + m_(t-1), i),
+// keep = exp(f + m_(t-1) - m_t), take = exp(i - m_t), exp(-m_t), and is made where it is used.
 __global__ void mlstm_maxima_kernel(float* __restrict__ gates, float* __restrict__ m_state, long long state_ld,
                                     const int* __restrict__ cu_q, const int* __restrict__ state_slots, int n_seqs, int H) {
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     pdl_launch_dependents();
     pdl_wait();
     if (idx >= n_seqs * H) return;
@@ -108,14 +167,30 @@ __global__ void mlstm_maxima_kernel(float* __restrict__ gates, float* __restrict
     const int slot = state_slots[s];
     float m = slot >= 0 ? m_state[(size_t)slot * state_ld + h] : 0.f;
     float4* g = reinterpret_cast<float4*>(gates);
-#pragma unroll 8
-    for (int j = 0; j < n; ++j) {
-        float4* at = g + (size_t)(q_beg + j) * H + h;
-        const float2 gate = *reinterpret_cast<const float2*>(at);
-        at->w = m;
-        m = fmaxf(gate.y + m, gate.x);
+    for (int t0 = 0; t0 < n; t0 += 32) {
+        const int nt = min(32, n - t0);
+        float4* at = g + (size_t)(q_beg + t0 + lane) * H + h;
+        float f = 0.f, i = -INFINITY;                     // beyond the sequence: the step that changes nothing
+        if (lane < nt) {
+            const float2 gate = *reinterpret_cast<const float2*>(at);
+            i = gate.x;
+            f = gate.y;
+        }
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float pf = __shfl_up_sync(0xffffffffu, f, o), pi = __shfl_up_sync(0xffffffffu, i, o);
+            if (lane >= o) {
+                i = fmaxf(pi + f, i);
+                f += pf;
+            }
+        }
+        const float after = fmaxf(f + m, i);
+        float before = __shfl_up_sync(0xffffffffu, after, 1);
+        if (lane == 0) before = m;
+        if (lane < nt) at->w = before;
+        m = __shfl_sync(0xffffffffu, after, nt - 1);
     }
-    if (slot >= 0) m_state[(size_t)slot * state_ld + h] = m;
+    if (slot >= 0 && lane == 0) m_state[(size_t)slot * state_ld + h] = m;
 }
 
 // ------------------------------------------------------------------------------------------------------- delta rule prep
@@ -170,7 +245,7 @@ __global__ void delta_rule_prep_kernel(float* __restrict__ aux, float* __restric
 // rows j, j + 16, ...  A chunk of TC tokens' vectors is staged in shared memory, then walked token by token.
 constexpr int LANES = 16;     // lanes that share a column
 constexpr int CT = 8;         // value columns a block
-constexpr int TC = 8;         // tokens a chunk
+constexpr int TC = 8;         // tokens a chunk: LANES * CT threads fetch one token's vectors by sixteen of them each
 enum { FORM_DELTA = 0, FORM_MLSTM = 1 };
 
 struct ScanParams {
@@ -195,6 +270,7 @@ __global__ void __launch_bounds__(LANES* CT) memory_scan_kernel(ScanParams p) {
     const int e = tile * CT + col;
     const bool live = e < E;
     // per token in the chunk: r [D], k [D], (delta) w [D], b [D], u [D]; v [CT]; scalars [4]
+    static_assert(TC * LANES == LANES * CT && CT + 4 <= LANES, "the staging's thread layout");
     const int vecs = FORM == FORM_DELTA ? 5 : 2;
     const int per_tok = vecs * D + CT + 4;
     pdl_launch_dependents();
@@ -215,36 +291,65 @@ __global__ void __launch_bounds__(LANES* CT) memory_scan_kernel(ScanParams p) {
     const T* kp = static_cast<const T*>(p.k);
     const T* vp = static_cast<const T*>(p.v);
     const int HD = H * D;
+    // Staging: thread (sj, sl) = (tid / 16, tid % 16) fetches, for token sj of a chunk, the values d = sl + 16 i of every vector
+    // (and one value column, one scalar); a chunk's values wait in registers while the chunk before is walked.
+    constexpr int VECS = FORM == FORM_DELTA ? 5 : 2;
+    const int sj = tid / LANES, sl = tid % LANES;
+    float stage[VECS * DPL], stage_v = 0.f, stage_s = 0.f;
+    auto fetch = [&](int c0) {
+        const int nt = min(TC, n - c0);
+        if (sj >= nt) return;
+        const size_t t = (size_t)(q_beg + c0 + sj);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int d = sl + LANES * i;
+            if (d < D) {
+                stage[i] = to_float(rp[t * p.ldr + (size_t)h * D + d]) * p.r_scale;
+                stage[DPL + i] = to_float(kp[t * p.ldk + (size_t)h * D + d]);
+                if (FORM == FORM_DELTA) {
+#pragma unroll
+                    for (int w = 0; w < 3; ++w) stage[(2 + w) * DPL + i] = p.aux[t * 3 * HD + (size_t)w * HD + (size_t)h * D + d];
+                }
+            }
+        }
+        if (sl < CT) {
+            const int ee = tile * CT + sl;
+            stage_v = ee < E ? to_float(vp[t * p.ldv + (size_t)h * E + ee]) : 0.f;
+        } else if (sl < CT + 4) {
+            const int q = sl - CT;
+            if (FORM == FORM_DELTA) {
+                stage_s = q < 2 ? p.dots[(t * H + h) * 2 + q] : 0.f;
+            } else {
+                // (i, f, (q . k) q_scale, m before the token) -> keep, take, exp(-m_t), take (q . k) q_scale
+                const float4 g = reinterpret_cast<const float4*>(p.dots)[t * H + h];
+                const float mn = fmaxf(g.y + g.w, g.x);
+                const float take = expf(g.x - mn);
+                stage_s = q == 0 ? expf(g.y + g.w - mn) : q == 1 ? take : q == 2 ? expf(-mn) : take * g.z;
+            }
+        }
+    };
+    auto put = [&](int c0) {
+        const int nt = min(TC, n - c0);
+        if (sj >= nt) return;
+        float* tk = sm + sj * per_tok;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int d = sl + LANES * i;
+            if (d < D) {
+#pragma unroll
+                for (int w = 0; w < VECS; ++w) tk[w * D + d] = stage[w * DPL + i];
+            }
+        }
+        if (sl < CT) tk[vecs * D + sl] = stage_v;
+        else if (sl < CT + 4) tk[vecs * D + sl] = stage_s;
+    };
+    fetch(0);
     for (int c0 = 0; c0 < n; c0 += TC) {
         const int nt = min(TC, n - c0);
         __syncthreads();
-        for (int i = tid; i < nt * per_tok; i += LANES * CT) {
-            const int j = i / per_tok, o = i % per_tok;
-            const size_t t = (size_t)(q_beg + c0 + j);
-            float val;
-            if (o < D) val = to_float(rp[t * p.ldr + (size_t)h * D + o]) * p.r_scale;
-            else if (o < 2 * D) val = to_float(kp[t * p.ldk + (size_t)h * D + (o - D)]);
-            else if (o < vecs * D) {
-                const int which = (o - 2 * D) / D, d = (o - 2 * D) % D;
-                val = p.aux[t * 3 * HD + (size_t)which * HD + (size_t)h * D + d];
-            } else if (o < vecs * D + CT) {
-                const int ee = tile * CT + (o - vecs * D);
-                val = ee < E ? to_float(vp[t * p.ldv + (size_t)h * E + ee]) : 0.f;
-            } else {
-                const int q = o - vecs * D - CT;
-                if (FORM == FORM_DELTA) {
-                    val = q < 2 ? p.dots[(t * H + h) * 2 + q] : 0.f;
-                } else {
-                    // (i, f, (q . k) q_scale, m before the token) -> keep, take, exp(-m_t), take (q . k) q_scale
-                    const float4 g = reinterpret_cast<const float4*>(p.dots)[t * H + h];
-                    const float mn = fmaxf(g.y + g.w, g.x);
-                    const float take = expf(g.x - mn);
-                    val = q == 0 ? expf(g.y + g.w - mn) : q == 1 ? take : q == 2 ? expf(-mn) : take * g.z;
-                }
-            }
-            sm[i] = val;
-        }
+        put(c0);
         __syncthreads();
+        if (c0 + TC < n) fetch(c0 + TC);
         for (int j = 0; j < nt; ++j) {
             const float* tk = sm + j * per_tok;
             const float* r_ = tk;
@@ -351,11 +456,24 @@ int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t st) {
 
 // out[t, c] = S_t * silu(g_t) with S_t = (1 - z) S_(t-1) + z cand over each sequence; zxg float32 [n, 3C] rows `ld` apart;
 // state [slots, >= C] float32 rows `state_ld` apart.
+// Steps of up to this many token rows walk token by token, a thread a channel; longer ones scan tiles of 32 tokens.
+constexpr int MIN_GRU_FEW_TOKENS = 64;
 LLMK_EXPORT int llmk_min_gru(void* out, const float* zxg, long long ld, const float* bz, const float* bx, float* state,
-                             long long state_ld, const int* cu_q, const int* state_slots, int n_seqs, int C, int dtype, void* stream) {
+                             long long state_ld, const int* cu_q, const int* state_slots, int n_seqs, int n_rows, int C, int dtype,
+                             void* stream) {
     if (n_seqs <= 0 || C <= 0) return LLMK_OK;
-    const dim3 grid(ceil_div(C, 128), n_seqs), block(128);
     cudaStream_t st = (cudaStream_t)stream;
+    if (n_rows > MIN_GRU_FEW_TOKENS) {
+        const dim3 tgrid(ceil_div(C, GT), n_seqs), tblock(GT * GT);
+        if (dtype == LLMK_F32)
+            LLMK_CHECK_LAUNCH_RC("min_gru", llmk_launch(min_gru_tile_kernel<float>, tgrid, tblock, 0, st, true, (float*)out, zxg, ld, bz, bx,
+                                                        state, state_ld, cu_q, state_slots, C));
+        else
+            LLMK_CHECK_LAUNCH_RC("min_gru", llmk_launch(min_gru_tile_kernel<bf16>, tgrid, tblock, 0, st, true, (bf16*)out, zxg, ld, bz, bx,
+                                                        state, state_ld, cu_q, state_slots, C));
+        return LLMK_OK;
+    }
+    const dim3 grid(ceil_div(C, 128), n_seqs), block(128);
     if (dtype == LLMK_F32)
         LLMK_CHECK_LAUNCH_RC("min_gru", llmk_launch(min_gru_kernel<float>, grid, block, 0, st, true, (float*)out, zxg, ld, bz, bx, state,
                                                     state_ld, cu_q, state_slots, C));
@@ -384,7 +502,7 @@ LLMK_EXPORT int llmk_mlstm_gates(float* gates, const void* q, long long ldq, con
         LLMK_CHECK_LAUNCH_RC("mlstm_gates", llmk_launch(mlstm_gates_kernel<bf16>, grid, block, 0, st, true, gates, (const bf16*)q, ldq,
                                                         (const bf16*)k, ldk, (const bf16*)gi, ldi, (const bf16*)gf, ldf, bi, bf, cu_q,
                                                         n_seqs, n_rows, H, D, cap, q_scale));
-    LLMK_CHECK_LAUNCH_RC("mlstm_maxima", llmk_launch(mlstm_maxima_kernel, dim3(ceil_div(n_seqs * H, 64)), dim3(64), 0, st, true, gates,
+    LLMK_CHECK_LAUNCH_RC("mlstm_maxima", llmk_launch(mlstm_maxima_kernel, dim3(ceil_div(n_seqs * H, 4)), dim3(128), 0, st, true, gates,
                                                      m_state, state_ld, cu_q, state_slots, n_seqs, H));
     return LLMK_OK;
 }

@@ -957,7 +957,7 @@ def min_gru(out: torch.Tensor, zxg: torch.Tensor, bias_z: Optional[torch.Tensor]
             or not out.is_contiguous():
         raise KernelError("min_gru: float32 [n, 3C] in, [n, C] out, float32 state rows of at least C")
     _check(lib, lib.llmk_min_gru(_ptr(out), _ptr(zxg), c_longlong(_row_stride(zxg)), _ptr(bias_z), _ptr(bias_x), _ptr(state),
-                                 c_longlong(_row_stride(state)), _ptr(cu_q), _ptr(state_slots), c_int(n_seqs), c_int(C),
+                                 c_longlong(_row_stride(state)), _ptr(cu_q), _ptr(state_slots), c_int(n_seqs), c_int(n), c_int(C),
                                  c_int(dtype_code(out.dtype)), _stream()))
 
 

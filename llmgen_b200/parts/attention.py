@@ -254,12 +254,8 @@ class GQAAttention(Mixer):
             longest = min(longest, self.window or self.chunk)
         by_sms = (2 * self.sm_count + blocks - 1) // blocks
         by_len = max(1, longest // 128)
-        parts = max(1, min(by_sms, by_len, 64))
-        if self.window:
-            # parts are ranges of absolute key positions: a window far into a long context
-            # would leave most of an even split empty, so windowed layers are not split
-            return 1, 0
-        return parts, 0
+        # under a window (as under a mask in blocks) the kernel cuts the keys a query can see, not the whole context
+        return max(1, min(by_sms, by_len, 64)), 0
 
     def workspace_bytes(self, tokens: int) -> int:
         """Bytes of activations this part keeps in the step's workspace for `tokens` rows: the packed projection

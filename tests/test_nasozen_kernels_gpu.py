@@ -149,8 +149,6 @@ def test_learned_sink_scores_enter_the_softmax_once_also_when_the_keys_come_in_p
             w = e / (e.sum() + math.exp(float(sinks[h]) - float(s.max())))
             want[h] = w @ v[first:, h // 2].double()
         for parts in (1, 3):
-            if parts > 1 and window:
-                continue
             out = torch.zeros(1, nq * vd, dtype=dt, device=DEV)
             scratch = torch.zeros(ops.attention_scratch_floats(1, nq, vd, parts), device=DEV) if parts > 1 else None
             ops.paged_attention(out, q.to(DEV), nq * hd, kc.to(DEV), vc.to(DEV), bt, pages, ctx_len, cu, tile_seq, tile_q0, 1, 1, nq, nkv, hd, page,
