@@ -192,7 +192,7 @@ class NasozenConfig:
                     r.check(start < stop <= len(parsed), f"loop [{start}, {stop}) does not lie within the {len(parsed)} layers")
                     loop = LoopConfig(start, stop, times)
         if streams is not None:
-            r.check(streams <= 8, f"streams {streams}: at most 8")
+            r.check(streams <= 16, f"streams {streams}: at most 16")
         r.finish()
         return cls(vocab, width, eps, mult, streams, tuple(parsed), loop, max_positions, dict(data))
 

@@ -441,9 +441,10 @@ LLMK_EXPORT int llmk_concat_stream(void* out, const float* resid, const void* de
 // streams [n, S, H] float32.  With y (an array of T, float32 slices, or a y + b y2): every stream is rewritten from all the old
 // ones, x_t <- sum_s mix[s * S + t] x_s + out_coef[t] y.  With next_in: normed[r, :] = rmsnorm(sum_t next_in[t] x_t) * next_gain
 // (the new streams), the input of the sublayer that follows.  Either half may be absent.  A block per token row.
-constexpr int MAX_STREAMS = 8;
+constexpr int MAX_STREAMS = 16;
 
-template <typename T>
+// MS: the most streams this instance takes (4, 8 or 16); the loops over streams are unrolled to it, except the outer one of 16.
+template <typename T, int MS>
 __global__ void __launch_bounds__(512) stream_step_kernel(float* __restrict__ streams, const void* __restrict__ y, int splits, long long split_stride,
                                    const void* __restrict__ y2, int splits2, long long split_stride2, float a, float b,
                                    const float* __restrict__ mix, const float* __restrict__ out_coef,
@@ -466,36 +467,32 @@ __global__ void __launch_bounds__(512) stream_step_kernel(float* __restrict__ st
     float* xs = streams + r * S * H;
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float x[MAX_STREAMS];
+        float x[MS];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s)
+        for (int s = 0; s < MS; ++s)
             if (s < S) x[s] = xs[(size_t)s * H + i];
+        float u = 0.f;
         if (y) {
             float v = load_sum<T>(y, r * H + i, splits, split_stride);
             if (y2) v = a * v + b * load_sum<T>(y2, r * H + i, splits2, split_stride2);
-            float nx[MAX_STREAMS];
-#pragma unroll
-            for (int t = 0; t < MAX_STREAMS; ++t) {
+            // every new stream from the old ones (x stays as it was read); the next sublayer's sum is taken on the way
+#pragma unroll(MS <= 8 ? MS : 1)
+            for (int t = 0; t < MS; ++t) {
                 if (t < S) {
                     float acc = coef[S * S + t] * v;
 #pragma unroll
-                    for (int s = 0; s < MAX_STREAMS; ++s)
+                    for (int s = 0; s < MS; ++s)
                         if (s < S) acc = fmaf(coef[s * S + t], x[s], acc);
-                    nx[t] = acc;
+                    xs[(size_t)t * H + i] = acc;
+                    u = fmaf(coef[S * S + S + t], acc, u);
                 }
             }
+        } else {
 #pragma unroll
-            for (int t = 0; t < MAX_STREAMS; ++t)
-                if (t < S) {
-                    x[t] = nx[t];
-                    xs[(size_t)t * H + i] = nx[t];
-                }
+            for (int t = 0; t < MS; ++t)
+                if (t < S) u = fmaf(coef[S * S + S + t], x[t], u);
         }
         if (next_in) {
-            float u = 0.f;
-#pragma unroll
-            for (int t = 0; t < MAX_STREAMS; ++t)
-                if (t < S) u = fmaf(coef[S * S + S + t], x[t], u);
             srow[i] = u;
             ss = fmaf(u, u, ss);
         }
@@ -519,16 +516,19 @@ LLMK_EXPORT int llmk_stream_step(float* streams, const void* y, int splits, long
     const int threads = H >= 2048 ? 512 : H >= 512 ? 256 : 128;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
+#define STREAM_STEP_LAUNCH(TYPE, MS)                                                                                                   \
+    do {                                                                                                                               \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(stream_step_kernel<TYPE, MS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        e = llmk_launch(stream_step_kernel<TYPE, MS>, dim3(n_rows), dim3(threads), smem, st, true, streams, y, splits, split_stride, y2, \
+                        splits2, split_stride2, a, b, mix, out_coef, next_in, next_gain, eps, (TYPE*)normed, S, H);                    \
+    } while (0)
     if (dtype == LLMK_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(stream_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = llmk_launch(stream_step_kernel<float>, dim3(n_rows), dim3(threads), smem, st, true, streams, y, splits, split_stride, y2, splits2,
-                        split_stride2, a, b, mix, out_coef, next_in, next_gain, eps, (float*)normed, S, H);
+        if (S <= 4) STREAM_STEP_LAUNCH(float, 4); else if (S <= 8) STREAM_STEP_LAUNCH(float, 8); else STREAM_STEP_LAUNCH(float, 16);
     } else if (dtype == LLMK_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(stream_step_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = llmk_launch(stream_step_kernel<bf16>, dim3(n_rows), dim3(threads), smem, st, true, streams, y, splits, split_stride, y2, splits2,
-                        split_stride2, a, b, mix, out_coef, next_in, next_gain, eps, (bf16*)normed, S, H);
+        if (S <= 4) STREAM_STEP_LAUNCH(bf16, 4); else if (S <= 8) STREAM_STEP_LAUNCH(bf16, 8); else STREAM_STEP_LAUNCH(bf16, 16);
     } else
         LLMK_FAIL("stream_step: unknown dtype %d", dtype);
+#undef STREAM_STEP_LAUNCH
     LLMK_CHECK_LAUNCH_RC("stream_step", e);
     return LLMK_OK;
 }

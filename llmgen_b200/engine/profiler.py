@@ -153,21 +153,25 @@ class ModelCost:
     def from_spec(cls, spec, w_elem: int = 2, kv_elem: int = 2) -> "ModelCost":
         n_mm, terms, complete = 0, [], True
         token_flops = state_bytes = 0
-        for item in spec.run_order:
-            block = spec.layers[item.layer]
-            mixer, ffn = getattr(block, "mixer", None), getattr(block, "ffn", None)
-            if getattr(mixer, "kind", None) == "attention":
+        def count(mixer, writes_cache) -> bool:
+            """Adds one mixer's products, attention terms, per-token work and state; False for a kind it does not know."""
+            nonlocal n_mm, token_flops, state_bytes
+            kind = getattr(mixer, "kind", None)
+            if kind == "attention":
                 q_dim, kv_dim = mixer.num_heads * mixer.head_dim, mixer.num_kv_heads * mixer.head_dim
-                n_mm += 2 * mixer.hidden_size * q_dim
-                if item.writes_cache:                       # an item that reads another's cache projects no k, v
-                    n_mm += 2 * mixer.hidden_size * kv_dim
-                terms.append(AttentionTerm(q_dim, kv_dim, int(mixer.window or 0)))
-            elif getattr(mixer, "kind", None) == "linear_attention":
+                v_dim, o_dim = mixer.num_kv_heads * mixer.value_dim, mixer.num_heads * mixer.value_dim
+                n_mm += mixer.hidden_size * (q_dim + o_dim)
+                if writes_cache:                            # an item that reads another's cache projects no k, v
+                    n_mm += mixer.hidden_size * (kv_dim + v_dim)
+                if mixer.gate_proj:
+                    n_mm += mixer.hidden_size * (mixer.num_heads if getattr(mixer, "gate_per_head", False) else o_dim)
+                terms.append(AttentionTerm((q_dim + o_dim) // 2, (kv_dim + v_dim) // 2, int(mixer.window or 0)))
+            elif kind == "linear_attention":
                 kd, vd = mixer.num_heads * mixer.key_dim, mixer.num_heads * mixer.value_dim
                 n_mm += mixer.hidden_size * (2 * kd + (3 if mixer.gate_proj else 2) * vd)
                 token_flops += 4 * mixer.num_heads * mixer.key_dim * mixer.value_dim       # the state's update and its product with q
                 state_bytes += 4 * mixer.num_heads * mixer.key_dim * mixer.value_dim
-            elif getattr(mixer, "kind", None) == "latent_attention":
+            elif kind == "latent_attention":
                 n, za = mixer.num_heads, mixer.kv_rank + mixer.rope_dim
                 n_mm += mixer.hidden_size * (mixer.q_rank + za + (2 if mixer.gate_proj else 1) * n * mixer.value_dim)
                 if getattr(mixer, "absorb_at_load", False):     # the query goes straight into the latent space
@@ -176,7 +180,30 @@ class ModelCost:
                     n_mm += mixer.q_rank * n * (mixer.nope_dim + mixer.rope_dim) + n * mixer.kv_rank * (mixer.nope_dim + mixer.value_dim)
                 # one shared entry of kv_rank + rope_dim values per token; per key and head 2 (za + kv_rank) flops
                 terms.append(AttentionTerm(n * (za + mixer.kv_rank) // 2, (za + 1) // 2, 0))
-            elif mixer is not None:
+            elif kind == "parallel":
+                return all([count(b, writes_cache) for b in mixer.branches])
+            elif kind == "min_gru":
+                n_mm += 4 * mixer.hidden_size * mixer.width
+                token_flops += 12 * mixer.width
+                state_bytes += 4 * mixer.width
+            elif kind == "mlstm":
+                kd, vd = mixer.num_heads * mixer.key_dim, mixer.num_heads * mixer.value_dim
+                n_mm += mixer.hidden_size * (2 * kd + 3 * vd + 2 * mixer.num_heads)
+                token_flops += 6 * mixer.num_heads * mixer.key_dim * mixer.value_dim       # read-out and update over the memory
+                state_bytes += 4 * (mixer.num_heads * mixer.key_dim * (mixer.value_dim + 1) + mixer.num_heads)
+            elif kind == "general_delta":
+                hd = mixer.num_heads * mixer.head_dim
+                n_mm += mixer.hidden_size * (6 * hd + mixer.decay_rank) + mixer.decay_rank * hd
+                token_flops += 8 * hd * mixer.head_dim                                     # two dot products over the memory, its update
+                state_bytes += 4 * hd * mixer.head_dim
+            else:
+                return False
+            return True
+
+        for item in spec.run_order:
+            block = spec.layers[item.layer]
+            mixer, ffn = getattr(block, "mixer", None), getattr(block, "ffn", None)
+            if mixer is not None and not count(mixer, item.writes_cache):
                 complete = False
             if getattr(ffn, "kind", None) == "gated_mlp":
                 n_mm += 3 * ffn.hidden_size * ffn.intermediate_size

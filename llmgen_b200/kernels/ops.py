@@ -858,7 +858,7 @@ def concat_stream(out: torch.Tensor, resid: torch.Tensor, delta, x0: torch.Tenso
 
 
 # ------------------------------------------------------------------------- several residual streams
-MAX_STREAMS = 8
+MAX_STREAMS = 16
 
 
 def stream_step(streams: torch.Tensor, y, mix: Optional[torch.Tensor], out_coef: Optional[torch.Tensor], next_in: Optional[torch.Tensor],

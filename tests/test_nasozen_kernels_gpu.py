@@ -35,7 +35,7 @@ def steps_of(*lens_of_steps):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("S,H", [(1, 40), (3, 36), (4, 260), (8, 48)])
+@pytest.mark.parametrize("S,H", [(1, 40), (3, 36), (4, 260), (8, 48), (12, 20)])
 def test_stream_step_rewrites_every_stream_from_the_old_ones_and_reads_for_the_next_sublayer(S, H, dtype):
     from llmgen_b200.kernels import ops
     dt, n = DT[dtype], 7
