@@ -24,7 +24,9 @@
 // Variations a model may switch on: values of another width than keys (`vd`); a bound on the scores,
 // s <- softcap * tanh(s / softcap) after the scale; a sink, one more term exp(0) in the softmax's denominator (a key of
 // score 0 that has no value: the weights of a row then sum to less than one; it enters once, when a row is finished or
-// its parts are merged); an output gate, out <- out * sigmoid(gate) element by element, applied as the row is written;
+// its parts are merged), or exp(z_h) with a learned score per head; an output gate, out <- out * sigmoid(gate) element by element or
+// one number per head, applied as the row is written; before the gate a head's row may be turned back in pairs (m, m + vd / 2) by minus
+// its query's position (values that were cached turned by theirs);
 // a mask in blocks of `chunk` positions counted from the sequence's start: a query sees the keys at or before it that lie
 // in its own block, floor(k / chunk) = floor(q / chunk) (with key parts, the visible keys of a single token are what is split).
 #define LLMK_MODULE_NAME "attention"
@@ -50,6 +52,9 @@ struct AttnParams {
     float* part_ml;
     const void* gate;        // [tokens, nq * vd] of the storage type, rows `gate_stride` apart, or null
     const float* sink_values;  // with `sink`: the sink's score per query head [nq]; null: 0 for every head
+    const float* turn_cos;     // [positions, vd / 2] (with turn_sin; vd 64 or 128): every head's row is turned back in pairs
+    const float* turn_sin;     // (m, m + vd / 2) by minus its query's position before the gate; null: rows leave as they are
+    int gate_heads;            // 1: the gate is one number per head, [tokens, nq]
     long long q_stride, o_stride, gate_stride;
     int max_blocks, nq, nkv, hd, vd, page_size, window, num_parts, part_size, bq, gc, chunks, sink, chunk;
     float scale, softcap;
@@ -253,7 +258,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
             }
         } else {
             T* o = static_cast<T*>(p.out) + tok * p.o_stride + (size_t)head_of[i] * vd;
-            const T* g = p.gate ? static_cast<const T*>(p.gate) + tok * p.gate_stride + (size_t)head_of[i] * vd : nullptr;
+            const T* g = p.gate ? static_cast<const T*>(p.gate) + tok * p.gate_stride + (size_t)head_of[i] * (p.gate_heads ? 1 : vd) : nullptr;
             float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
             if (p.sink && l[i] > 0.f) {
                 // the sink's score is z (0 unless the heads have learned ones): with M = max(m, z), weights are
@@ -263,10 +268,35 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
                 const float w = expf(m[i] - M);
                 inv = w / (l[i] * w + expf(z - M));
             }
+            if (p.gate_heads && g) inv *= gate_of(to_float(g[0]));
+            if (p.turn_cos) {
+                // vd is 64 or 128: the value half a head on from d = lane + 32 j is this lane's own, one or two registers on
+                const int qpos = first_pos + qi_of[i];
+                const float* cs = p.turn_cos + (size_t)qpos * (vd / 2);
+                const float* sn = p.turn_sin + (size_t)qpos * (vd / 2);
+                if constexpr (HDL >= 2) {
+                    if (vd == 64) {
+                        const float lo = acc[i][0], hi = acc[i][1];
+                        acc[i][0] = lo * cs[lane] + hi * sn[lane];
+                        acc[i][1] = hi * cs[lane] - lo * sn[lane];
+                    }
+                }
+                if constexpr (HDL >= 4) {
+                    if (vd == 128) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const int d = lane + 32 * j;
+                            const float lo = acc[i][j], hi = acc[i][j + 2];
+                            acc[i][j] = lo * cs[d] + hi * sn[d];
+                            acc[i][j + 2] = hi * cs[d] - lo * sn[d];
+                        }
+                    }
+                }
+            }
 #pragma unroll
             for (int j = 0; j < HDL; ++j) {
                 const int d = lane + 32 * j;
-                if (d < vd) o[d] = from_float<T>(acc[i][j] * inv * (g ? gate_of(to_float(g[d])) : 1.f));
+                if (d < vd) o[d] = from_float<T>(acc[i][j] * inv * ((g && !p.gate_heads) ? gate_of(to_float(g[d])) : 1.f));
             }
         }
     }
@@ -276,7 +306,9 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
 template <typename T>
 __global__ void attention_reduce_kernel(T* __restrict__ out, long long o_stride, const float* __restrict__ part_o,
                                         const float* __restrict__ part_ml, int n_rows, int nq, int hd,
-                                        int num_parts, int sink, const float* __restrict__ sink_values, const T* __restrict__ gate, long long gate_stride) {
+                                        int num_parts, int sink, const float* __restrict__ sink_values, const T* __restrict__ gate, long long gate_stride,
+                                        int gate_heads, const float* __restrict__ turn_cos, const float* __restrict__ turn_sin,
+                                        const int* __restrict__ positions) {
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= n_rows) return;
@@ -290,16 +322,29 @@ __global__ void attention_reduce_kernel(T* __restrict__ out, long long o_stride,
     for (int pt = 0; pt < num_parts; ++pt)
         if (ml[2 * pt + 1] > 0.f) denom += expf(ml[2 * pt] - M) * ml[2 * pt + 1];
     if (sink && denom > 0.f) denom += expf(z - M);
-    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+    float inv = denom > 0.f ? 1.0f / denom : 0.f;
     const size_t tok = (size_t)(row / nq), head = (size_t)(row % nq);
     T* o = out + tok * o_stride + head * hd;
-    const T* g = gate ? gate + tok * gate_stride + head * hd : nullptr;
-    for (int d = lane; d < hd; d += 32) {
+    const T* g = gate ? gate + tok * gate_stride + head * (gate_heads ? 1 : hd) : nullptr;
+    if (g && gate_heads) inv *= gate_of(to_float(g[0]));
+    auto merged = [&](int d) {
         float v = 0.f;
         for (int pt = 0; pt < num_parts; ++pt)
             if (ml[2 * pt + 1] > 0.f) v += expf(ml[2 * pt] - M) * part_o[((size_t)row * num_parts + pt) * hd + d];
-        o[d] = from_float<T>(v * inv * (g ? gate_of(to_float(g[d])) : 1.f));
+        return v;
+    };
+    if (turn_cos) {
+        // every head's row turned back in pairs (d, d + hd / 2) by minus the query's position
+        const int half = hd / 2, pos = positions[tok];
+        for (int d = lane; d < half; d += 32) {
+            const float lo = merged(d), hi = merged(d + half);
+            const float c = turn_cos[(size_t)pos * half + d], sv = turn_sin[(size_t)pos * half + d];
+            o[d] = from_float<T>((lo * c + hi * sv) * inv * ((g && !gate_heads) ? gate_of(to_float(g[d])) : 1.f));
+            o[d + half] = from_float<T>((hi * c - lo * sv) * inv * ((g && !gate_heads) ? gate_of(to_float(g[d + half])) : 1.f));
+        }
+        return;
     }
+    for (int d = lane; d < hd; d += 32) o[d] = from_float<T>(merged(d) * inv * ((g && !gate_heads) ? gate_of(to_float(g[d])) : 1.f));
 }
 
 static int hdl_of(int hd) { return hd <= 32 ? 1 : hd <= 64 ? 2 : hd <= 128 ? 4 : hd <= 256 ? 8 : 16; }
@@ -346,7 +391,8 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
                                      const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int hd,
                                      int page_size, int window, float scale, int num_parts, int part_size,
                                      void* scratch, int vd, float softcap, int sink, const float* sink_values, const void* gate,
-                                     long long gate_stride, int chunk, int dtype, void* stream) {
+                                     long long gate_stride, int chunk, int gate_heads, const float* turn_cos, const float* turn_sin,
+                                     const int* positions, int dtype, void* stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return LLMK_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0) LLMK_FAIL("paged_attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
     if (hd <= 0 || hd > 512) LLMK_FAIL("paged_attention: head_dim %d must be positive, at most 512", hd);
@@ -355,6 +401,7 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
     if (softcap < 0.f) LLMK_FAIL("paged_attention: softcap %g", (double)softcap);
     if (page_size <= 0) LLMK_FAIL("paged_attention: page_size %d", page_size);
     if (chunk < 0) LLMK_FAIL("paged_attention: blocks of %d positions", chunk);
+    if (turn_cos && ((vd != 64 && vd != 128) || !turn_sin || !positions)) LLMK_FAIL("paged_attention: rows are turned back for value widths 64 and 128, with sin and positions");
     if (num_parts < 1 || (num_parts > 1 && !scratch)) LLMK_FAIL("paged_attention: bad split (%d parts, scratch %p)", num_parts, scratch);
     if (num_parts > 65535 || nkv > 65535) LLMK_FAIL("paged_attention: grid too large");
     AttnParams p;
@@ -366,7 +413,8 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
     p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
     p.q_stride = q_stride; p.o_stride = o_stride; p.max_blocks = max_blocks;
     p.nq = nq; p.nkv = nkv; p.hd = hd; p.vd = vd; p.page_size = page_size; p.window = window;
-    p.softcap = softcap; p.sink = sink ? 1 : 0; p.sink_values = sink_values; p.gate = gate; p.gate_stride = gate_stride; p.chunk = chunk;
+    p.softcap = softcap; p.sink = sink ? 1 : 0; p.sink_values = sink_values; p.gate_heads = gate_heads ? 1 : 0;
+    p.turn_cos = (turn_cos && turn_sin) ? turn_cos : nullptr; p.turn_sin = turn_sin; p.gate = gate; p.gate_stride = gate_stride; p.chunk = chunk;
     p.num_parts = num_parts; p.part_size = part_size; p.scale = scale;
     p.part_o = (float*)scratch;
     p.part_ml = num_parts > 1 ? (float*)scratch + (size_t)n_tokens * nq * num_parts * vd : nullptr;
@@ -388,10 +436,10 @@ LLMK_EXPORT int llmk_paged_attention(void* out, long long o_stride, const void* 
         const int blocks = ceil_div(n_rows, warps);
         if (dtype == LLMK_F32)
             attention_reduce_kernel<float><<<blocks, warps * 32, 0, s>>>((float*)out, o_stride, p.part_o, p.part_ml, n_rows, nq, vd, num_parts,
-                                                                         p.sink, sink_values, (const float*)gate, gate_stride);
+                                                                         p.sink, sink_values, (const float*)gate, gate_stride, p.gate_heads, p.turn_cos, p.turn_sin, positions);
         else
             attention_reduce_kernel<bf16><<<blocks, warps * 32, 0, s>>>((bf16*)out, o_stride, p.part_o, p.part_ml, n_rows, nq, vd, num_parts,
-                                                                        p.sink, sink_values, (const bf16*)gate, gate_stride);
+                                                                        p.sink, sink_values, (const bf16*)gate, gate_stride, p.gate_heads, p.turn_cos, p.turn_sin, positions);
         LLMK_CHECK_LAUNCH("attention_reduce");
     }
     return LLMK_OK;

@@ -29,6 +29,9 @@ struct Params {
     bf16* out;
     const bf16* gate;
     const float* sink_values;     // with `sink`: the sink's score per query head [nq]; null: 0
+    const float* turn_cos;        // [positions, VD / 2] (with turn_sin): every head's row is turned back in pairs (m, m + VD / 2) by minus
+    const float* turn_sin;        // its query's position before the gate; null: rows leave as they are
+    int gate_heads;               // 1: the gate is one number per head, [tokens, nq]
     const int* block_tables;
     const int* ctx_len;
     const int* cu_q;
@@ -250,12 +253,29 @@ __global__ void __launch_bounds__(WARPS * 32) attention_mma_kernel(Params p) {
         }
         const size_t tok = (size_t)(q_beg + q0 + row);
         bf16* dst = p.out + tok * p.o_stride + (size_t)head * VD;
-        const bf16* gt = p.gate ? p.gate + tok * p.gate_stride + (size_t)head * VD : nullptr;
+        const bf16* gt = p.gate ? p.gate + tok * p.gate_stride + (size_t)head * (p.gate_heads ? 1 : VD) : nullptr;
+        const float head_gate = (gt && p.gate_heads) ? 1.0f / (1.0f + expf(-__bfloat162float(gt[0]))) : 1.f;
+        if (p.turn_cos) {
+            // the thread holds columns n * 8 + 2 tq (+ 1) for every n: a column and the one half a head on are both its own
+            const float* cs = p.turn_cos + (size_t)qpos[r] * (VD / 2);
+            const float* sn = p.turn_sin + (size_t)qpos[r] * (VD / 2);
+#pragma unroll
+            for (int n = 0; n < VD / 16; ++n) {
+                const int col = n * 8 + 2 * tq;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float lo = o[n][2 * r + e], hi = o[n + VD / 16][2 * r + e];
+                    const float c = cs[col + e], sv = sn[col + e];
+                    o[n][2 * r + e] = lo * c + hi * sv;
+                    o[n + VD / 16][2 * r + e] = hi * c - lo * sv;
+                }
+            }
+        }
 #pragma unroll
         for (int n = 0; n < VD / 8; ++n) {
             const int col = n * 8 + 2 * tq;
-            float v0 = o[n][2 * r] * inv, v1 = o[n][2 * r + 1] * inv;
-            if (gt) {
+            float v0 = o[n][2 * r] * inv * head_gate, v1 = o[n][2 * r + 1] * inv * head_gate;
+            if (gt && !p.gate_heads) {
                 v0 *= 1.0f / (1.0f + expf(-__bfloat162float(gt[col])));
                 v1 *= 1.0f / (1.0f + expf(-__bfloat162float(gt[col + 1])));
             }
@@ -292,7 +312,8 @@ LLMK_EXPORT int llmk_attention_mma(void* out, long long o_stride, const void* q,
                                    const void* vcache, const int* block_tables, int max_blocks, const int* ctx_len, const int* cu_q,
                                    const int* tile_seq, const int* tile_q0, int n_tiles, int nq, int nkv, int hd, int vd,
                                    int page_size, int window, float scale, float softcap, int sink, const float* sink_values, const void* gate,
-                                   long long gate_stride, int chunk, void* stream) {
+                                   long long gate_stride, int chunk, int gate_heads, const float* turn_cos, const float* turn_sin,
+                                   void* stream) {
     if (n_tiles <= 0) return LLMK_OK;
     if (llmk_attention_mma_tile_queries(nq, nkv, hd, vd) == 0)
         LLMK_FAIL("attention_mma: not taken (heads %d/%d, key width %d and value width %d must be 64 or 128)", nq, nkv, hd, vd);
@@ -302,7 +323,8 @@ LLMK_EXPORT int llmk_attention_mma(void* out, long long o_stride, const void* q,
     if (nq > 65535) LLMK_FAIL("attention_mma: grid too large");
     Params p;
     p.q = (const bf16*)q; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache; p.out = (bf16*)out;
-    p.gate = (const bf16*)gate; p.sink_values = sink_values; p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q;
+    p.gate = (const bf16*)gate; p.sink_values = sink_values; p.gate_heads = gate_heads ? 1 : 0;
+    p.turn_cos = (turn_cos && turn_sin) ? turn_cos : nullptr; p.turn_sin = turn_sin; p.block_tables = block_tables; p.ctx_len = ctx_len; p.cu_q = cu_q;
     p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.q_stride = q_stride; p.o_stride = o_stride; p.gate_stride = gate_stride;
     p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.sink = sink ? 1 : 0; p.chunk = chunk > 0 ? chunk : 0;
     p.scale = scale; p.softcap = softcap;

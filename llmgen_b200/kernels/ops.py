@@ -539,20 +539,40 @@ def _check_sinks(who: str, sink: bool, sink_values: Optional[torch.Tensor], nq: 
         raise KernelError(f"{who}: the sinks' scores are one float32 per query head, with `sink` set")
 
 
+ATTENTION_TURN_WIDTHS = (64, 128)    # value widths whose rows the attention kernels turn back themselves
+
+
+def _check_turn(who: str, turn_back, positions, vd: int, gate, gate_per_head: bool, nq: int):
+    if gate is not None and gate_per_head and gate.shape[1] != nq:
+        raise KernelError(f"{who}: a gate per head is [tokens, heads]")
+    if turn_back is None:
+        return None, None
+    cos, sin = turn_back
+    if vd not in ATTENTION_TURN_WIDTHS or positions is None or cos.dtype != torch.float32 or sin.dtype != torch.float32 \
+            or cos.shape[1] != vd // 2 or tuple(sin.shape) != tuple(cos.shape) or not cos.is_contiguous() or not sin.is_contiguous():
+        raise KernelError(f"{who}: rows are turned back for value widths {ATTENTION_TURN_WIDTHS}, by float32 tables [positions, vd / 2]")
+    return cos, sin
+
+
 def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
                     block_tables: torch.Tensor, max_blocks: int, ctx_len: torch.Tensor, cu_q: torch.Tensor,
                     tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, n_tokens: int, nq: int, nkv: int,
                     hd: int, page_size: int, window: int, scale: float, num_parts: int = 1, part_size: int = 0,
                     scratch: Optional[torch.Tensor] = None, vd: int = 0, softcap: float = 0.0, sink: bool = False,
-                    gate: Optional[torch.Tensor] = None, chunk: int = 0, sink_values: Optional[torch.Tensor] = None) -> None:
+                    gate: Optional[torch.Tensor] = None, chunk: int = 0, sink_values: Optional[torch.Tensor] = None,
+                    gate_per_head: bool = False, turn_back: Optional[tuple] = None, positions: Optional[torch.Tensor] = None) -> None:
     """out[t, nq*vd] = causal GQA of q[t] over the paged cache (see csrc/attention.cu).  `vd`: the values' width where
     it differs from `hd`; `softcap` > 0 bounds the scores by softcap * tanh(s / softcap); `sink` adds exp(0) to the
-    softmax's denominator (exp(sink_values[head]) with `sink_values`, float32 [nq]); `gate` [tokens, nq*vd] (storage dtype): the result is multiplied by sigmoid(gate); `chunk` > 0:
+    softmax's denominator (exp(sink_values[head]) with `sink_values`, float32 [nq]); `gate` [tokens, nq*vd] (storage dtype): the result is multiplied by sigmoid(gate)
+    (`gate_per_head`: [tokens, nq], one number per head); `turn_back` = (cos, sin) float32 [positions, vd / 2] with `positions` (the
+    tokens' positions): each head's row is turned back in pairs (m, m + vd / 2) by minus its position before the gate (value widths
+    `ATTENTION_TURN_WIDTHS`); `chunk` > 0:
     a query sees the keys at or before it inside its own block of that many positions, counted from the sequence's start."""
     lib = build.load("attention")
     if gate is not None and gate.dtype != q.dtype:
         raise KernelError("paged_attention: the gate has the storage dtype")
     _check_sinks("paged_attention", sink, sink_values, nq)
+    tcos, tsin = _check_turn("paged_attention", turn_back, positions, vd or hd, gate, gate_per_head, nq)
     if num_parts > 1:
         need = attention_scratch_floats(n_tokens, nq, vd or hd, num_parts)
         if scratch is None or scratch.numel() < need or scratch.dtype != torch.float32:
@@ -564,6 +584,7 @@ def paged_attention(out: torch.Tensor, q: torch.Tensor, q_stride: int, kcache: t
                                          c_int(window), c_float(scale), c_int(num_parts), c_int(part_size),
                                          _ptr(scratch), c_int(vd), c_float(softcap), c_int(1 if sink else 0), _ptr(sink_values),
                                          _ptr(gate), c_longlong(_row_stride(gate) if gate is not None else 0), c_int(chunk),
+                                         c_int(1 if gate_per_head else 0), _ptr(tcos), _ptr(tsin), _ptr(positions),
                                          c_int(dtype_code(q.dtype)), _stream()),
            2 if num_parts > 1 else 1)
 
@@ -577,18 +598,20 @@ def attention_mma(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcac
                   max_blocks: int, ctx_len: torch.Tensor, cu_q: torch.Tensor, tile_seq: torch.Tensor, tile_q0: torch.Tensor,
                   n_tiles: int, nq: int, nkv: int, hd: int, vd: int, page_size: int, window: int, scale: float,
                   softcap: float = 0.0, sink: bool = False, gate: Optional[torch.Tensor] = None, chunk: int = 0,
-                  sink_values: Optional[torch.Tensor] = None) -> None:
+                  sink_values: Optional[torch.Tensor] = None, gate_per_head: bool = False, turn_back: Optional[tuple] = None) -> None:
     """Prompt portions in bfloat16 with 32-bit softmax weights on the tensor cores (csrc/attention_mma.cu): the same
     result as `paged_attention` with these options, tiles of `attention_mma_tile_queries` queries."""
     lib = build.load("attention_mma")
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or (gate is not None and gate.dtype != torch.bfloat16):
         raise KernelError("attention_mma: bfloat16 only")
     _check_sinks("attention_mma", sink, sink_values, nq)
+    tcos, tsin = _check_turn("attention_mma", turn_back, ctx_len, vd, gate, gate_per_head, nq)
     _check(lib, lib.llmk_attention_mma(_ptr(out), c_longlong(_row_stride(out)), _ptr(q), c_longlong(_row_stride(q)), _ptr(kcache),
                                        _ptr(vcache), _ptr(block_tables), c_int(max_blocks), _ptr(ctx_len), _ptr(cu_q), _ptr(tile_seq),
                                        _ptr(tile_q0), c_int(n_tiles), c_int(nq), c_int(nkv), c_int(hd), c_int(vd), c_int(page_size),
                                        c_int(window), c_float(scale), c_float(softcap), c_int(1 if sink else 0), _ptr(sink_values),
-                                       _ptr(gate), c_longlong(_row_stride(gate) if gate is not None else 0), c_int(chunk), _stream()))
+                                       _ptr(gate), c_longlong(_row_stride(gate) if gate is not None else 0), c_int(chunk),
+                                       c_int(1 if gate_per_head else 0), _ptr(tcos), _ptr(tsin), _stream()))
 
 
 def attention_decode_set_cluster_merge(on: bool) -> None:

@@ -369,8 +369,9 @@ class GQAAttention(Mixer):
     def _forward_row_norms(self, ctx, x, cache, group, cos, sin, rot):
         """A layer whose q and k are normed over their whole projections: the packed projection [q | k | v | gate], the short
         convolution over the channels of q, k, v (float32 out; its history from and to the request's state), one kernel for both
-        norms, the rotation of q and k, the rotation of v and the cache write, attention with the heads' sink scores, and one
-        kernel that turns each head's output back and applies the head's gate."""
+        norms, the rotation of q and k, the rotation of v and the cache write, and attention with the heads' sink scores, which
+        turns each head's output back and applies the head's gate as it writes a row (value widths 64 and 128; one more kernel
+        does that for other widths)."""
         T, ws = ctx.n_tokens, ctx.workspace
         if not cache.writes:
             raise ValueError("attention: a layer with norms over whole projections writes its own cache")
@@ -395,14 +396,19 @@ class GQAAttention(Mixer):
         ops.attn_prep_rows(rows, q, cache.k, cache.v, ctx.positions, group.slots, cos, sin, vcos, vsin, self.q_gain, self.k_gain,
                            nq, nk, hd, vd, rot, cache.page_size, self.norm_eps)
         o = ws.buffer("attn_o", T, nq * vd, self.dtype)
-        per_head = self.spec.gate_per_head
-        inside = None if per_head else gate          # a gate per value is applied inside the attention kernels
+        per_head = bool(self.spec.gate_per_head and gate is not None)
+        # value widths 64 and 128: the attention kernels turn a head's row back and apply the head's gate as they write it;
+        # other widths leave that to one more kernel
+        inside = vd in ops.ATTENTION_TURN_WIDTHS or (vcos is None and not per_head)
+        turn = (vcos, vsin) if (inside and vcos is not None) else None
+        kgate = gate if (inside or not per_head) else None
         mma_bq = 0 if ctx.pure_decode else self.mma_tile_queries()
         if mma_bq and ctx.has_array(f"attention_tiles_bq{mma_bq}_seq"):
             tile_seq = ctx.array(f"attention_tiles_bq{mma_bq}_seq")
             ops.attention_mma(o, q, cache.k, cache.v, group.block_tables, group.max_blocks, ctx.ctx_len, ctx.cu_q, tile_seq,
                               ctx.array(f"attention_tiles_bq{mma_bq}_q0"), tile_seq.numel(), nq, nk, hd, vd, cache.page_size, self.window,
-                              float(self.spec.scale), sink=self.sink, gate=inside, sink_values=self.sink_scores)
+                              float(self.spec.scale), sink=self.sink, gate=kgate, sink_values=self.sink_scores,
+                              gate_per_head=per_head and kgate is not None, turn_back=turn)
         else:
             tile_seq = ctx.array(self.tiles_name + "_seq")
             tile_q0 = ctx.array(self.tiles_name + "_q0")
@@ -412,9 +418,10 @@ class GQAAttention(Mixer):
                 scratch = ws.flat("attn_split", ops.attention_scratch_floats(T, nq, vd, parts), torch.float32)
             ops.paged_attention(o, q, q.stride(0), cache.k, cache.v, group.block_tables, group.max_blocks, ctx.ctx_len, ctx.cu_q,
                                 tile_seq, tile_q0, tile_seq.numel(), T, nq, nk, hd, cache.page_size, self.window,
-                                float(self.spec.scale), parts, part_size, scratch, vd=vd, sink=self.sink, gate=inside,
-                                sink_values=self.sink_scores)
-        if vcos is not None or (per_head and gate is not None):
+                                float(self.spec.scale), parts, part_size, scratch, vd=vd, sink=self.sink, gate=kgate,
+                                sink_values=self.sink_scores, gate_per_head=per_head and kgate is not None, turn_back=turn,
+                                positions=ctx.positions)
+        if not inside:
             ops.unrotate_gate(o, gate if per_head else None, ctx.positions, vcos, vsin, nq, vd)
         out = linear_sliced(ws, "mixer_out", o, self.w_o, self.dtype)
         if self.o_bias is not None:

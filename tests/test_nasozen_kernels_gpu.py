@@ -265,3 +265,41 @@ def test_the_generalized_delta_rule_step_by_step(H, D, dtype):
     for i, slot in enumerate((2, 0, 3)):
         close(state[slot, :hd * D], st[i].reshape(-1), tol)
     assert float(state[1].min()) == 7.0 and float(state[:, hd * D].abs().sum()) == 7.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("vd", [64, 128])
+def test_the_attention_kernel_turns_a_row_back_and_applies_the_gate_of_its_head(vd, dtype):
+    """Value widths that the kernels finish themselves: the weighted sum of a head is turned back by minus the query's position
+    and multiplied by one gate per head, in one part and when key parts are merged."""
+    from llmgen_b200.kernels import ops
+    dt, nq, nkv, hd, page, n_keys, base = DT[dtype], 4, 2, 16, 16, 200, 40.0
+    tol = 2e-5 if dtype == "float32" else 2e-2
+    k, v = rnd((n_keys, nkv, hd), 1, 1.0, dt), rnd((n_keys, nkv, vd), 2, 1.0, dt)
+    q, gate = rnd((1, nq * hd), 3, 1.0, dt), rnd((1, nq), 4, 1.0, dt)
+    sinks = torch.tensor([-1.0, 0.5, 2.0, 0.0])
+    pages = (n_keys + page - 1) // page
+    kc, vc = torch.zeros(pages, nkv, page, hd, dtype=dt), torch.zeros(pages, nkv, page, vd, dtype=dt)
+    for j in range(n_keys):
+        kc[j // page, :, j % page], vc[j // page, :, j % page] = k[j], v[j]
+    ang = torch.arange(256, dtype=torch.float64)[:, None] * base ** (-2.0 * torch.arange(vd // 2, dtype=torch.float64) / vd)
+    cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    bt = torch.arange(pages, dtype=torch.int32, device=DEV)
+    ctx_len = torch.tensor([n_keys], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    one = torch.tensor([0], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n_keys - 1], dtype=torch.int32, device=DEV)
+    want = torch.zeros(nq, vd, dtype=torch.float64)
+    for h in range(nq):
+        s = (k[:, h // 2].double() @ q[0, h * hd:(h + 1) * hd].double()) * 0.25
+        e = torch.exp(s - s.max())
+        w = e / (e.sum() + math.exp(float(sinks[h]) - float(s.max())))
+        row = plain.turn_halves(w @ v[:, h // 2].double(), n_keys - 1, vd, base, sign=-1.0)
+        want[h] = row * torch.sigmoid(gate[0, h].double())
+    for parts in (1, 2):
+        out = torch.zeros(1, nq * vd, dtype=dt, device=DEV)
+        scratch = torch.zeros(ops.attention_scratch_floats(1, nq, vd, parts), device=DEV) if parts > 1 else None
+        ops.paged_attention(out, q.to(DEV), nq * hd, kc.to(DEV), vc.to(DEV), bt, pages, ctx_len, cu, one, one, 1, 1, nq, nkv, hd, page, 0, 0.25,
+                            parts, 0, scratch, vd=vd, sink=True, sink_values=sinks.to(DEV), gate=gate.to(DEV), gate_per_head=True,
+                            turn_back=(cos, sin), positions=pos)
+        close(out.view(nq, vd), want, tol)
