@@ -242,7 +242,7 @@ __global__ void delta_rule_prep_kernel(float* __restrict__ aux, float* __restric
 
 // ------------------------------------------------------------------------------------------------------- memory scan
 // A block per (tile of CT value columns, head, sequence); sixteen lanes share a column of S, lane j of them holding key
-// rows j, j + 16, ...  A chunk of TC tokens' vectors is staged in shared memory, then walked token by token.
+// rows j DPL .. j DPL + DPL - 1.  A chunk of TC tokens' vectors is staged in shared memory, then walked token by token.
 constexpr int LANES = 16;     // lanes that share a column
 constexpr int CT = 8;         // value columns a block
 constexpr int TC = 8;         // tokens a chunk: LANES * CT threads fetch one token's vectors by sixteen of them each
@@ -261,12 +261,49 @@ struct ScanParams {
     float r_scale, den_eps;
 };
 
-template <typename T, int FORM, int DPL>
+// A value's bits in a 32-bit register (a 16-bit load extends into one by itself), and back.
+// The loads are volatile asm so that they are issued where they stand, a chunk ahead of their use, and not moved down to it.
+__device__ __forceinline__ uint32_t load_bits(const float* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t load_bits(const bf16* p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+template <typename T> __device__ __forceinline__ float bits_value(uint32_t b);
+template <> __device__ __forceinline__ float bits_value<float>(uint32_t b) { return __uint_as_float(b); }
+template <> __device__ __forceinline__ float bits_value<bf16>(uint32_t b) { return __uint_as_float(b << 16); }
+
+// A lane's DPL rows of one of a token's vectors (rows l DPL ..), zeros beyond D; sixteen bytes at a time where the sizes allow.
+template <int DPL>
+__device__ __forceinline__ void lane_rows(float (&dst)[DPL], const float* __restrict__ src, int l, int D, bool vec4) {
+    if (DPL % 4 == 0 && vec4) {
+#pragma unroll
+        for (int i4 = 0; i4 < DPL / 4; ++i4) {
+            const int d = l * DPL + 4 * i4;
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (d < D) t = *reinterpret_cast<const float4*>(src + d);
+            dst[4 * i4] = t.x; dst[4 * i4 + 1] = t.y; dst[4 * i4 + 2] = t.z; dst[4 * i4 + 3] = t.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int d = l * DPL + i;
+            dst[i] = d < D ? src[d] : 0.f;
+        }
+    }
+}
+
+// FULL: the key width is exactly 16 DPL (a compile-time number then: no row of a lane lies beyond it).
+template <typename T, int FORM, int DPL, bool FULL>
 __global__ void __launch_bounds__(LANES* CT) memory_scan_kernel(ScanParams p) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int tile = blockIdx.x, h = blockIdx.y, s = blockIdx.z;
     const int tid = threadIdx.x, l = tid % LANES, col = tid / LANES;
-    const int D = p.D, E = p.E, H = p.H;
+    const int D = FULL ? LANES * DPL : p.D, E = p.E, H = p.H;
     const int e = tile * CT + col;
     const bool live = e < E;
     // per token in the chunk: r [D], k [D], (delta) w [D], b [D], u [D]; v [CT]; scalars [4]
@@ -280,22 +317,26 @@ __global__ void __launch_bounds__(LANES* CT) memory_scan_kernel(ScanParams p) {
     const int slot = p.state_slots[s];
     float* Sg = slot >= 0 ? p.state + (size_t)slot * p.state_ld + (size_t)h * D * E : nullptr;
     float* ng = (slot >= 0 && FORM == FORM_MLSTM) ? p.state + (size_t)slot * p.state_ld + (size_t)H * D * E + (size_t)h * D : nullptr;
+    // lane l of a column holds key rows l DPL .. l DPL + DPL - 1 (rows beyond D stay zero: their vectors are read as zeros)
+    const bool vec4 = DPL % 4 == 0 && (FULL || D % 4 == 0);
     float S[DPL], nv[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
-        const int d = l + LANES * i;
+        const int d = l * DPL + i;
         S[i] = (Sg && live && d < D) ? Sg[(size_t)d * E + e] : 0.f;
         nv[i] = (ng && d < D) ? ng[d] : 0.f;
     }
     const T* rp = static_cast<const T*>(p.r);
     const T* kp = static_cast<const T*>(p.k);
     const T* vp = static_cast<const T*>(p.v);
-    const int HD = H * D;
+    const int HD = H * D, HE = H * E;
+    float* out_col = p.out + (size_t)q_beg * HE + (size_t)h * E + e;
     // Staging: thread (sj, sl) = (tid / 16, tid % 16) fetches, for token sj of a chunk, the values d = sl + 16 i of every vector
     // (and one value column, one scalar); a chunk's values wait in registers while the chunk before is walked.
-    constexpr int VECS = FORM == FORM_DELTA ? 5 : 2;
     const int sj = tid / LANES, sl = tid % LANES;
-    float stage[VECS * DPL], stage_v = 0.f, stage_s = 0.f;
+    uint32_t raw_rk[2 * DPL], raw_v = 0;                // a value's bits as loaded, one register each: nothing here waits for a load; `put` converts
+    float raw_aux[(FORM == FORM_DELTA ? 3 : 1) * DPL], raw_s = 0.f;
+    float4 raw_g = make_float4(0.f, 0.f, 0.f, 0.f);
     auto fetch = [&](int c0) {
         const int nt = min(TC, n - c0);
         if (sj >= nt) return;
@@ -304,28 +345,20 @@ __global__ void __launch_bounds__(LANES* CT) memory_scan_kernel(ScanParams p) {
         for (int i = 0; i < DPL; ++i) {
             const int d = sl + LANES * i;
             if (d < D) {
-                stage[i] = to_float(rp[t * p.ldr + (size_t)h * D + d]) * p.r_scale;
-                stage[DPL + i] = to_float(kp[t * p.ldk + (size_t)h * D + d]);
+                raw_rk[i] = load_bits(rp + t * p.ldr + (size_t)h * D + d);
+                raw_rk[DPL + i] = load_bits(kp + t * p.ldk + (size_t)h * D + d);
                 if (FORM == FORM_DELTA) {
 #pragma unroll
-                    for (int w = 0; w < 3; ++w) stage[(2 + w) * DPL + i] = p.aux[t * 3 * HD + (size_t)w * HD + (size_t)h * D + d];
+                    for (int w = 0; w < 3; ++w) raw_aux[w * DPL + i] = __uint_as_float(load_bits(p.aux + t * 3 * HD + (size_t)w * HD + (size_t)h * D + d));
                 }
             }
         }
         if (sl < CT) {
             const int ee = tile * CT + sl;
-            stage_v = ee < E ? to_float(vp[t * p.ldv + (size_t)h * E + ee]) : 0.f;
+            if (ee < E) raw_v = load_bits(vp + t * p.ldv + (size_t)h * E + ee);
         } else if (sl < CT + 4) {
-            const int q = sl - CT;
-            if (FORM == FORM_DELTA) {
-                stage_s = q < 2 ? p.dots[(t * H + h) * 2 + q] : 0.f;
-            } else {
-                // (i, f, (q . k) q_scale, m before the token) -> keep, take, exp(-m_t), take (q . k) q_scale
-                const float4 g = reinterpret_cast<const float4*>(p.dots)[t * H + h];
-                const float mn = fmaxf(g.y + g.w, g.x);
-                const float take = expf(g.x - mn);
-                stage_s = q == 0 ? expf(g.y + g.w - mn) : q == 1 ? take : q == 2 ? expf(-mn) : take * g.z;
-            }
+            if (FORM == FORM_DELTA) raw_s = sl - CT < 2 ? p.dots[(t * H + h) * 2 + (sl - CT)] : 0.f;
+            else raw_g = reinterpret_cast<const float4*>(p.dots)[t * H + h];
         }
     };
     auto put = [&](int c0) {
@@ -336,12 +369,28 @@ __global__ void __launch_bounds__(LANES* CT) memory_scan_kernel(ScanParams p) {
         for (int i = 0; i < DPL; ++i) {
             const int d = sl + LANES * i;
             if (d < D) {
+                tk[d] = bits_value<T>(raw_rk[i]) * p.r_scale;
+                tk[D + d] = bits_value<T>(raw_rk[DPL + i]);
+                if (FORM == FORM_DELTA) {
 #pragma unroll
-                for (int w = 0; w < VECS; ++w) tk[w * D + d] = stage[w * DPL + i];
+                    for (int w = 0; w < 3; ++w) tk[(2 + w) * D + d] = raw_aux[w * DPL + i];
+                }
             }
         }
-        if (sl < CT) tk[vecs * D + sl] = stage_v;
-        else if (sl < CT + 4) tk[vecs * D + sl] = stage_s;
+        if (sl < CT) {
+            tk[vecs * D + sl] = tile * CT + sl < E ? bits_value<T>(raw_v) : 0.f;
+        } else if (sl < CT + 4) {
+            const int q = sl - CT;
+            float val = raw_s;
+            if (FORM == FORM_MLSTM) {
+                // (i, f, (q . k) q_scale, m before the token) -> keep, take, exp(-m_t), take (q . k) q_scale
+                const float4 g = raw_g;
+                const float mn = fmaxf(g.y + g.w, g.x);
+                const float take = expf(g.x - mn);
+                val = q == 0 ? expf(g.y + g.w - mn) : q == 1 ? take : q == 2 ? expf(-mn) : take * g.z;
+            }
+            tk[vecs * D + sl] = val;
+        }
     };
     fetch(0);
     for (int c0 = 0; c0 < n; c0 += TC) {
@@ -350,24 +399,23 @@ __global__ void __launch_bounds__(LANES* CT) memory_scan_kernel(ScanParams p) {
         put(c0);
         __syncthreads();
         if (c0 + TC < n) fetch(c0 + TC);
-        for (int j = 0; j < nt; ++j) {
+        auto walk = [&](int j) {
             const float* tk = sm + j * per_tok;
-            const float* r_ = tk;
-            const float* k_ = tk + D;
             const float v_e = tk[vecs * D + col];
             const float* sc = tk + vecs * D + CT;
+            float rr[DPL], kk[DPL];
+            lane_rows<DPL>(rr, tk, l, D, vec4);
+            lane_rows<DPL>(kk, tk + D, l, D, vec4);
             if (FORM == FORM_DELTA) {
-                const float* w_ = tk + 2 * D;
-                const float* b_ = tk + 3 * D;
-                const float* u_ = tk + 4 * D;
+                float ww[DPL], bb[DPL], uu[DPL];
+                lane_rows<DPL>(ww, tk + 2 * D, l, D, vec4);
+                lane_rows<DPL>(bb, tk + 3 * D, l, D, vec4);
+                lane_rows<DPL>(uu, tk + 4 * D, l, D, vec4);
                 float seen = 0.f, read = 0.f;
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) {
-                    const int d = l + LANES * i;
-                    if (d < D) {
-                        seen = fmaf(u_[d], S[i], seen);
-                        read = fmaf(w_[d] * r_[d], S[i], read);
-                    }
+                    seen = fmaf(uu[i], S[i], seen);
+                    read = fmaf(ww[i] * rr[i], S[i], read);
                 }
 #pragma unroll
                 for (int o = LANES / 2; o > 0; o >>= 1) {
@@ -375,21 +423,15 @@ __global__ void __launch_bounds__(LANES* CT) memory_scan_kernel(ScanParams p) {
                     read += __shfl_xor_sync(0xffffffffu, read, o);
                 }
 #pragma unroll
-                for (int i = 0; i < DPL; ++i) {
-                    const int d = l + LANES * i;
-                    if (d < D) S[i] = fmaf(k_[d], v_e, fmaf(w_[d], S[i], -b_[d] * seen));
-                }
-                if (l == 0 && live) p.out[(size_t)(q_beg + c0 + j) * H * E + (size_t)h * E + e] = read - sc[0] * seen + sc[1] * v_e;
+                for (int i = 0; i < DPL; ++i) S[i] = fmaf(kk[i], v_e, fmaf(ww[i], S[i], -bb[i] * seen));
+                if (l == 0 && live) out_col[(size_t)(c0 + j) * HE] = read - sc[0] * seen + sc[1] * v_e;
             } else {
                 const float keep = sc[0], take = sc[1], em = sc[2], kq = sc[3];
                 float read = 0.f, nq = 0.f;
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) {
-                    const int d = l + LANES * i;
-                    if (d < D) {
-                        read = fmaf(r_[d], S[i], read);
-                        nq = fmaf(r_[d], nv[i], nq);
-                    }
+                    read = fmaf(rr[i], S[i], read);
+                    nq = fmaf(rr[i], nv[i], nq);
                 }
 #pragma unroll
                 for (int o = LANES / 2; o > 0; o >>= 1) {
@@ -398,32 +440,36 @@ __global__ void __launch_bounds__(LANES* CT) memory_scan_kernel(ScanParams p) {
                 }
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) {
-                    const int d = l + LANES * i;
-                    if (d < D) {
-                        const float tk_d = take * k_[d];
-                        S[i] = fmaf(tk_d, v_e, keep * S[i]);
-                        nv[i] = fmaf(keep, nv[i], tk_d);
-                    }
+                    const float tk_d = take * kk[i];
+                    S[i] = fmaf(tk_d, v_e, keep * S[i]);
+                    nv[i] = fmaf(keep, nv[i], tk_d);
                 }
                 if (l == 0 && live) {
                     const float num = fmaf(keep, read, kq * v_e);
                     const float den = fmaxf(fabsf(fmaf(keep, nq, kq)), em) + p.den_eps;
-                    p.out[(size_t)(q_beg + c0 + j) * H * E + (size_t)h * E + e] = num / den;
+                    out_col[(size_t)(c0 + j) * HE] = num / den;
                 }
             }
+        };
+        if (nt == TC) {
+            // a whole chunk, unrolled: a token's reads of shared memory stand beside the shuffles of the token before
+#pragma unroll
+            for (int j = 0; j < TC; ++j) walk(j);
+        } else {
+            for (int j = 0; j < nt; ++j) walk(j);
         }
     }
     if (Sg && live) {
 #pragma unroll
         for (int i = 0; i < DPL; ++i) {
-            const int d = l + LANES * i;
+            const int d = l * DPL + i;
             if (d < D) Sg[(size_t)d * E + e] = S[i];
         }
     }
     if (ng && tile == 0 && col == 0) {
 #pragma unroll
         for (int i = 0; i < DPL; ++i) {
-            const int d = l + LANES * i;
+            const int d = l * DPL + i;
             if (d < D) ng[d] = nv[i];
         }
     }
@@ -435,17 +481,13 @@ int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t st) {
     const size_t smem = (size_t)TC * (vecs * p.D + CT + 4) * sizeof(float);
     const dim3 grid(ceil_div(p.E, CT), p.H, n_seqs), block(LANES * CT);
     const int dpl = ceil_div(p.D, LANES);
-#define SCAN_CASE(N)                                                                                                       \
-    if (dpl <= N) {                                                                                                        \
-        static bool configured = false;                                                                                    \
-        if (!configured && smem > 48 * 1024) {                                                                             \
-            cudaError_t e = cudaFuncSetAttribute(memory_scan_kernel<T, FORM, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                                 (int)(TC * (5 * 256 + CT + 4) * sizeof(float)));                          \
-            if (e != cudaSuccess) LLMK_FAIL("memory_scan: cannot raise shared memory: %s", cudaGetErrorString(e));        \
-            configured = true;                                                                                             \
-        }                                                                                                                  \
-        LLMK_CHECK_LAUNCH_RC("memory_scan", llmk_launch(memory_scan_kernel<T, FORM, N>, grid, block, smem, st, true, p)); \
-        return LLMK_OK;                                                                                                    \
+#define SCAN_CASE(N)                                                                                                           \
+    if (dpl <= N) {                                                                                                            \
+        if (p.D == LANES * N)                                                                                                  \
+            LLMK_CHECK_LAUNCH_RC("memory_scan", llmk_launch(memory_scan_kernel<T, FORM, N, true>, grid, block, smem, st, true, p)); \
+        else                                                                                                                   \
+            LLMK_CHECK_LAUNCH_RC("memory_scan", llmk_launch(memory_scan_kernel<T, FORM, N, false>, grid, block, smem, st, true, p)); \
+        return LLMK_OK;                                                                                                        \
     }
     SCAN_CASE(1) SCAN_CASE(2) SCAN_CASE(4) SCAN_CASE(8) SCAN_CASE(16)
 #undef SCAN_CASE
