@@ -85,9 +85,9 @@ def nasozen_config(s: dict) -> dict:
             "rot": {"base": 500000.0, "dims": hd // 2}}
     par = {"type": "parallel", "mixer": {"left": left, "right": {"width": W}, "left_scale": 1.0, "right_scale": 0.5}, "mlp": routed}
     rule = {"type": "general_delta", "mixer": {"heads": W // 64, "dim": 64, "decay_rank": 64}, "mlp": routed}
-    memory = {"type": "mlstm", "mixer": {"heads": max(1, heads // 2), "dim": hd, "vdim": hd, "gate_cap": 15.0}, "mlp": dense}
+    memory = {"type": "mlstm", "mixer": {"heads": max(1, heads // 2), "dim": hd, "vdim": hd, "gate_cap": 12.0}, "mlp": dense}
     layers = ([par, rule, par, memory] * s["layers"])[: s["layers"]]
-    return {"architecture": "Nasozen", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6}, "residual_mult": 0.7, "streams": 4,
+    return {"architecture": "Nasozen", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6}, "residual_mult": 0.8, "streams": 4,
             "layers": layers, "max_positions": CONTEXT}
 
 

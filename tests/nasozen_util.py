@@ -87,7 +87,7 @@ WIDE = config([
 TENSOR = config([
     parallel(left(6, 3, 64, 64, 0.11, 3, window=96, rot=(10000.0, 32)), 32, moe(4, 2, 64)),
     parallel(left(2, 1, 128, 64, 0.09, 2, window=40, rot=(500.0, 128)), 16, None),
-    parallel(left(2, 2, 64, 128, 0.125, 4, window=130, rot=(250000.0, 16)), 24, None),
+    parallel(left(2, 2, 64, 128, 0.125, 4, window=130, rot=(200000.0, 16)), 24, None),
 ], width=64, vocab=97, streams=2)
 # One parallel layer whose weights `plant_needle` rewrites so that one token's query finds one other token's key.
 NEEDLE_WINDOW = 40
